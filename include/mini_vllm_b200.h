@@ -1,0 +1,169 @@
+/*
+ * C ABI of libmini_vllm_b200.so: the B200 (sm_100a) kernels for mini-vllm's ragged
+ * continuous-batching attention path.
+ *
+ * Conventions for every entry point
+ *   - All data pointers are DEVICE pointers owned by the caller (typically PyTorch tensors
+ *     kept alive until the stream reaches the launch).  Nothing here allocates, frees,
+ *     synchronises or throws; work is enqueued on `stream` (a cudaStream_t passed as void*).
+ *   - Return value: 0 on success, a negative mvb_status for an argument error found on the
+ *     host (nothing is launched in that case).
+ *   - `dev_status` (optional, may be NULL) is a device int32[4] the caller zeroes; a kernel
+ *     that meets an out-of-range slot / block id / position, or whose bounded wait runs out,
+ *     records {code, detail, block, thread} there, skips the access and carries on.
+ *   - bf16 tensors are passed as void*; the last dimension (head_dim) is contiguous and
+ *     heads are contiguous (stride head_dim); only the token (row) stride is free.
+ *   - KV pool layout per layer: [num_blocks, block_size, num_kv_heads, head_dim] bf16,
+ *     contiguous, the layout the reference allocates in
+ *     minivllm/executor/executor.py:51-60.  A slot is block_id * block_size + offset.
+ *
+ * Reference citations are paths inside w4096/mini-vllm.
+ */
+#ifndef MINI_VLLM_B200_H_
+#define MINI_VLLM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum mvb_status {
+  MVB_OK = 0,
+  MVB_INVALID_ARGUMENT = -1,
+  MVB_UNSUPPORTED_SHAPE = -2,
+  MVB_LAUNCH_FAILED = -3,
+  MVB_TENSOR_MAP_FAILED = -4,
+  MVB_MISALIGNED = -5,
+  MVB_NO_DRIVER_ENTRY = -6
+};
+
+/* Library ABI version (bumped when a signature changes). */
+int mvb_abi_version(void);
+/* Human-readable name of a status code. */
+const char* mvb_status_string(int status);
+
+/*
+ * Prefill batch packing on the device.
+ * Replaces Executor._build_prefill_input (minivllm/executor/executor.py:81-127) and
+ * Executor._build_block_table (:156-163): from per-sequence facts it expands
+ *   input_ids[t], positions[t] = cached + i, slot_mapping[t] = blocks[pos/bs]*bs + pos%bs,
+ *   cu_seqlens_q / cu_seqlens_k (exclusive prefix sums, int32 [num_seqs+1]) and, when
+ *   block_table != NULL, the [num_seqs, table_width] table right-padded with -1.
+ * Inputs (device int32): seq_len[num_seqs] (full length n), cached_len[num_seqs],
+ *   blk_off[num_seqs+1] (exclusive prefix sum of per-sequence block counts),
+ *   blocks_flat[blk_off[num_seqs]], new_tokens[num_tokens] (the uncached suffixes, concatenated).
+ * A token whose block index is beyond its sequence's block list (warm-up requests own no
+ * blocks, executor.py:62-78) gets slot -1.
+ */
+int mvb_pack_prefill(const int32_t* seq_len, const int32_t* cached_len, const int32_t* blk_off,
+                     const int32_t* blocks_flat, const int32_t* new_tokens, int num_seqs, int num_tokens,
+                     int table_width, int block_size, int64_t* input_ids, int64_t* positions,
+                     int32_t* slot_mapping, int32_t* cu_seqlens_q, int32_t* cu_seqlens_k, int32_t* block_table,
+                     int32_t* dev_status, void* stream);
+
+/*
+ * Decode batch packing on the device, written straight into (slices of) the CUDA-graph
+ * runner's static buffers.
+ * Replaces Executor._build_decode_input (minivllm/executor/executor.py:130-153) and the staging
+ * copies of CudaGraphRunner.replay (minivllm/executor/graph.py:64-70).
+ * For row b < num_seqs: input_ids = token, positions = n-1, cache_seqlens = n,
+ *   slot = last_block*bs + (n - (nblk-1)*bs) - 1, block_table[b, :table_width] = blocks, pad -1.
+ * Rows num_seqs..padded_seqs-1 are padding: input_ids 0, positions 0, slot -1, cache_seqlens 0,
+ *   block table row -1.
+ * The token of row b is prev_sampled[src_index[b]] when prev_sampled != NULL and
+ * src_index[b] >= 0 (the previous step's sampler output, still on the device), else
+ * host_tokens[b].
+ * block_table has row stride table_stride (>= table_width) elements.
+ */
+int mvb_pack_decode(const int32_t* seq_len, const int32_t* blk_off, const int32_t* blocks_flat,
+                    const int32_t* host_tokens, const int64_t* prev_sampled, const int32_t* src_index,
+                    int num_seqs, int padded_seqs, int table_width, int64_t table_stride, int block_size,
+                    int64_t* input_ids, int64_t* positions, int32_t* slot_mapping, int32_t* cache_seqlens,
+                    int32_t* block_table, int32_t* dev_status, void* stream);
+
+/*
+ * Fused rotary embedding + paged KV-cache write.
+ * Replaces RotaryEmbedding.forward (minivllm/models/layers/rotary.py:49-71) followed by
+ * store_kvcache (minivllm/models/layers/attention.py:13-43).
+ *   q [num_tokens, num_q_heads, head_dim] bf16, row stride q_row_stride elements: rotated in place.
+ *   k [num_tokens, num_kv_heads, head_dim]: rotated; written to k_cache at slot_mapping[t]
+ *     (skipped when the slot is -1 or slot_mapping == NULL) and, if k_in_place != 0, back into k.
+ *   v: copied to v_cache at the same slot.
+ *   cos_sin [max_pos, head_dim] fp32 = cat(cos, sin) as built by rotary.py:32-47; NULL disables
+ *     the rotation (plain store_kvcache).  Arithmetic is fp32 with separately rounded products,
+ *     one rounding to bf16, so results are bit-identical to the eager reference.
+ * head_dim must be a multiple of 16; k_cache/v_cache may be NULL only with slot_mapping NULL.
+ */
+int mvb_rope_kv_write(void* q, int64_t q_row_stride, void* k, int64_t k_row_stride, const void* v,
+                      int64_t v_row_stride, const int64_t* positions, const float* cos_sin, int64_t max_pos,
+                      const int32_t* slot_mapping, void* k_cache, void* v_cache, int64_t num_slots,
+                      int num_tokens, int num_q_heads, int num_kv_heads, int head_dim, int k_in_place,
+                      int32_t* dev_status, void* stream);
+
+/*
+ * Paged decode attention (one query token per sequence), split along the context.
+ * Replaces flash_attn_with_kvcache as called at minivllm/models/layers/attention.py:90-91.
+ *
+ * mvb_decode_workspace_bytes: size of the caller-supplied workspace for up to max_seqs rows.
+ * mvb_decode_plan: one small launch per step (the plan depends only on cache_seqlens and the
+ *   window, so every layer of a step shares it) that balances 16-token tiles over the
+ *   persistent grid and records it in the workspace.
+ * mvb_decode_attn: q [num_seqs, num_q_heads, head_dim] -> out (same shape, bf16).  Key j of
+ *   sequence b is visible iff max(0, n-1-window_left) <= j < n with n = cache_seqlens[b]
+ *   (window_left < 0: no window).  Rows with n == 0 (graph padding, graph.py:66-69) give zeros.
+ *   Grid and pointers do not depend on data, so the launch sequence can be captured in a
+ *   CUDA graph.  block_table is [num_seqs, table_width] with row stride table_stride.
+ *   Supported: head_dim 128 or 256; num_q_heads/num_kv_heads <= 8; num_kv_heads in {1,2,4} or a
+ *   multiple of 8 (head_dim 128) / 4 (head_dim 256); block_size a multiple of 16.
+ *   The plan must have been made for the same cache_seqlens, window and head shape.
+ */
+size_t mvb_decode_workspace_bytes(int max_seqs, int num_q_heads, int head_dim);
+int mvb_decode_plan(const int32_t* cache_seqlens, int num_seqs, int window_left, int num_q_heads,
+                    int num_kv_heads, int head_dim, void* workspace, size_t workspace_bytes, void* stream);
+int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                    int64_t num_blocks, int block_size, const int32_t* cache_seqlens,
+                    const int32_t* block_table, int64_t table_stride, int table_width, int num_seqs,
+                    int num_q_heads, int num_kv_heads, int head_dim, float scale, int window_left, void* out,
+                    int64_t out_row_stride, void* workspace, size_t workspace_bytes, int32_t* dev_status,
+                    void* stream);
+
+/*
+ * Causal varlen prefill attention on the tcgen05 tensor cores.
+ * Replaces flash_attn_varlen_func as called at minivllm/models/layers/attention.py:84-87.
+ *   q [total_q, num_q_heads, head_dim]; sequence s owns rows cu_seqlens_q[s]..cu_seqlens_q[s+1].
+ *   block_table == NULL: k, v are dense [total_k, num_kv_heads, head_dim] (row stride
+ *     kv_row_stride) sliced by cu_seqlens_k.
+ *   block_table != NULL: k, v are the paged pool (kv_rows = num_blocks*block_size slots,
+ *     kv_row_stride = num_kv_heads*head_dim) and keys 0..k_len-1 of sequence s are gathered
+ *     through row s of the table (the prefix-cache case, attention.py:79-83).
+ *   Query i of a sequence sits at position p = k_len - q_len + i and sees keys
+ *   max(0, p - window_left) <= j <= p.
+ * Supported: head_dim 128 (256 planned), any GQA ratio, block_size a multiple of 128.
+ */
+int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void* k, const void* v, int64_t kv_row_stride,
+                     int64_t kv_rows, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                     const int32_t* block_table, int64_t table_stride, int block_size, int num_seqs,
+                     int total_q, int max_seqlen_q, int num_q_heads, int num_kv_heads, int head_dim,
+                     float scale, int window_left, void* out, int64_t out_row_stride, int32_t* dev_status,
+                     void* stream);
+
+/*
+ * Fused temperature / top-k / Gumbel-max sampler over the vocabulary.
+ * Replaces Sampler.forward (minivllm/models/layers/sampler.py:9-31).
+ *   logits [num_rows, vocab] bf16 (row stride in elements) -> out int64 [num_rows].
+ *   top_k == NULL: greedy argmax of logits / temperature (lowest index wins ties), the
+ *     reference's path when no top-k/top-p is requested (sampler.py:31).
+ *   top_k != NULL: row r keeps every logit >= its top_k[r]-th largest (top_k[r] <= 0 keeps
+ *     all), adds Gumbel noise from Philox4x32-10 keyed by (seed, offset, r, column) to
+ *     logit / temperature, and returns the argmax.  temperatures may be NULL (all 1).
+ */
+int mvb_sample(const void* logits, int64_t row_stride, int num_rows, int vocab, const float* temperatures,
+               const int32_t* top_k, uint64_t seed, uint64_t offset, int64_t* out, int32_t* dev_status,
+               void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MINI_VLLM_B200_H_ */

@@ -1,0 +1,18 @@
+// Version and status strings of the C ABI.
+#include "common.cuh"
+#include "mini_vllm_b200.h"
+
+extern "C" int mvb_abi_version(void) { return 1; }
+
+extern "C" const char* mvb_status_string(int status) {
+  switch (status) {
+    case MVB_OK: return "ok";
+    case MVB_INVALID_ARGUMENT: return "invalid argument";
+    case MVB_UNSUPPORTED_SHAPE: return "unsupported shape";
+    case MVB_LAUNCH_FAILED: return "kernel launch failed";
+    case MVB_TENSOR_MAP_FAILED: return "tensor map encoding failed";
+    case MVB_MISALIGNED: return "pointer or stride not aligned";
+    case MVB_NO_DRIVER_ENTRY: return "cuTensorMapEncodeTiled not available from the driver";
+    default: return "unknown status";
+  }
+}

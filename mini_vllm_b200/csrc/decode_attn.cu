@@ -1,0 +1,542 @@
+// Split-context paged decode attention for sm_100a (HBM-bound).
+//
+// Work unit: a "CTA tile" of CT tokens of one sequence, all KV heads of a head group.  A
+// one-CTA plan kernel (once per step; every layer reuses it) prefix-sums the tile counts and
+// hands each of the P persistent CTAs a contiguous range of tiles, so the load is balanced to
+// within one tile whatever the ragged lengths are, the grid never depends on data (CUDA-graph
+// capturable) and a sequence is split only where a CTA boundary falls inside it.
+//
+// Inside a CTA every warp owns one KV head (and one 16-token sub-tile when there are more
+// warps than heads) and runs its own TMA -> shared-memory ring: the lane-0 thread issues
+// 128-byte-swizzled bulk tensor loads of K and V rows gathered through the block table, the
+// warp waits on the stage's mbarrier, and then
+//     S^T[16 tok x 8 heads] = K[16 x D] . Q^T      (mma.sync m16n8k16, A = K via ldmatrix)
+//     online softmax down the token axis            (quad shuffles xor 4/8/16)
+//     O^T[D x 8 heads]     += V^T[D x 16] . P^T     (A = V via ldmatrix.trans, B = P^T via movmatrix)
+// so the G query heads of a GQA group share each loaded K/V tile and the accumulators cost
+// D/4 registers per thread.  The arithmetic is a few percent of the issue slots; the kernel is
+// bound by the K/V stream: algorithmic bytes = sum_b visible_tokens(b) * 2 * Hkv * D * 2.
+//
+// A segment (the part of a sequence inside one CTA's range) that covers the whole sequence is
+// normalised and written straight to the output; otherwise the CTA writes a partial
+// (normalised O in fp32 + log2-sum-exp) and the combine kernel, a separate launch, merges the
+// partials.  No kernel ever waits on another CTA.
+#include "common.cuh"
+#include "host_util.cuh"
+#include "mini_vllm_b200.h"
+#include "scan.cuh"
+
+namespace mvb {
+
+constexpr int kMaxCtas = 160;          // workspace is sized for this many persistent CTAs
+constexpr int kPlanThreads = 256;
+constexpr int kMinTilesPerCta = 2;
+
+struct DecodeHeader {                  // first 32 bytes of the workspace (device memory)
+  int32_t total_tiles, per_cta, num_ctas, cta_tokens, num_seqs, window_left, pad0, pad1;
+};
+
+struct DecodeLayout {                  // byte offsets inside the workspace
+  size_t first_seq, lse, o, tile_prefix, total;
+};
+
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+static DecodeLayout decode_layout(int max_seqs, int hq, int d) {
+  DecodeLayout l;
+  l.first_seq = sizeof(DecodeHeader);
+  l.lse = align_up(l.first_seq + sizeof(int32_t) * (kMaxCtas + 1), 256);
+  l.o = align_up(l.lse + sizeof(float) * kMaxCtas * 2 * hq, 256);
+  l.tile_prefix = align_up(l.o + sizeof(float) * kMaxCtas * 2 * static_cast<size_t>(hq) * d, 256);
+  l.total = align_up(l.tile_prefix + sizeof(int32_t) * (static_cast<size_t>(max_seqs) + 1), 256);
+  return l;
+}
+
+template <int D, int HPC>
+struct DecodeCfg {
+  static constexpr int NW = (D == 128) ? 8 : 4;       // warps per CTA
+  static constexpr int TS = NW / HPC;                 // 16-token sub-tiles per CTA tile
+  static constexpr int CT = TS * 16;                  // tokens per CTA tile
+  static constexpr int NSTAGES = 3;
+  static constexpr int HALVES = D / 64;               // 64-element (128-byte) column halves
+  static constexpr int TILE_BYTES = 16 * D * 2;       // K (or V) rows of one sub-tile
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  static constexpr int FIN_STRIDE = D + 4;            // floats per (warp, head): O[D], m, l
+  static_assert(NW % HPC == 0, "warps must divide evenly over the heads of a CTA");
+};
+
+static int cta_tokens_for(int hkv, int d) {
+  const int nw = d == 128 ? 8 : 4;
+  const int hpc = hkv < nw ? hkv : nw;
+  return (nw / hpc) * 16;
+}
+
+// ---- plan -------------------------------------------------------------------------------------
+__device__ __forceinline__ int visible_start(int n, int window_left) {
+  return window_left >= 0 ? max(0, n - 1 - window_left) : 0;
+}
+
+__global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int32_t* __restrict__ cache_seqlens,
+                                                                   int num_seqs, int window_left, int cta_tokens,
+                                                                   int num_ctas, DecodeHeader* hdr,
+                                                                   int32_t* first_seq, int32_t* tile_prefix) {
+  block_exclusive_scan<kPlanThreads>(
+      [&](int b) {
+        const int n = cache_seqlens[b];
+        if (n <= 0) return 0;
+        const int start_al = visible_start(n, window_left) / cta_tokens * cta_tokens;
+        return (n - start_al + cta_tokens - 1) / cta_tokens;
+      },
+      num_seqs, tile_prefix);
+  const int total = tile_prefix[num_seqs];
+  int per = (total + num_ctas - 1) / num_ctas;
+  per = per < kMinTilesPerCta ? kMinTilesPerCta : per;
+  if (threadIdx.x == 0) {
+    hdr->total_tiles = total; hdr->per_cta = per; hdr->num_ctas = num_ctas; hdr->cta_tokens = cta_tokens;
+    hdr->num_seqs = num_seqs; hdr->window_left = window_left; hdr->pad0 = 0; hdr->pad1 = 0;
+  }
+  for (int c = threadIdx.x; c <= num_ctas; c += kPlanThreads) {
+    const int64_t t = static_cast<int64_t>(c) * per;
+    int b = num_seqs;
+    if (t < total) {                   // last b with tile_prefix[b] <= t
+      int lo = 0, hi = num_seqs;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tile_prefix[mid] <= t) lo = mid; else hi = mid;
+      }
+      b = lo;
+    }
+    first_seq[c] = b;
+  }
+}
+
+// ---- main kernel ------------------------------------------------------------------------------
+struct DecodeParams {
+  const __nv_bfloat16* q;
+  int64_t q_stride;
+  __nv_bfloat16* out;
+  int64_t out_stride;
+  const int32_t* cache_seqlens;
+  const int32_t* block_table;
+  int64_t table_stride;
+  int table_width;
+  int num_seqs, hq, group, block_size;
+  int64_t num_blocks;
+  float scale_log2;
+  int window_left;
+  const DecodeHeader* hdr;
+  const int32_t* first_seq;
+  const int32_t* tile_prefix;
+  float* part_lse;
+  float* part_o;
+  int* dev_status;
+};
+
+struct SeqView {
+  int b, tp0, tp1, n, start, start_al;
+};
+
+template <int CT>
+__device__ __forceinline__ void load_seq(SeqView& s, int b, const DecodeParams& p) {
+  s.b = b;
+  s.tp0 = p.tile_prefix[b];
+  s.tp1 = p.tile_prefix[b + 1];
+  s.n = p.cache_seqlens[b];
+  s.start = visible_start(s.n, p.window_left);
+  s.start_al = s.start / CT * CT;
+}
+
+template <int D, int HPC>
+__global__ void __launch_bounds__(DecodeCfg<D, HPC>::NW * 32, 1)
+decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                   const DecodeParams p) {
+  using C = DecodeCfg<D, HPC>;
+  constexpr int NW = C::NW, CT = C::CT, NST = C::NSTAGES;
+  constexpr uint32_t FULL = 0xffffffffu;
+  extern __shared__ uint8_t smem_raw[];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head_local = warp % HPC, sub = warp / HPC;
+  const int kvh = blockIdx.y * HPC + head_local;
+  const int G = p.group;
+  const int c = blockIdx.x;
+  const int total = p.hdr->total_tiles, per = p.hdr->per_cta;
+  const int t0 = c * per;
+  if (t0 >= total) return;                                   // CTA-uniform
+  const int t1 = min(total, t0 + per);
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t my_stages = base + warp * (NST * C::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + NW * NST * C::STAGE_BYTES) + warp * NST;
+  float* fin = reinterpret_cast<float*>(base_ptr + NW * NST * C::STAGE_BYTES + NW * NST * sizeof(uint64_t));
+
+  if (lane == 0) {
+    tma_prefetch_desc(&k_map);
+    tma_prefetch_desc(&v_map);
+#pragma unroll
+    for (int s = 0; s < NST; ++s) mbar_init(&bars[s], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  // ---- producer side: the same tile walk as the consumer, NST-1 tiles ahead --------------------
+  SeqView fs;
+  load_seq<CT>(fs, p.first_seq[c], p);
+  int ft = t0, nfetch = 0, blk_base = -1, blk_reg = -1;
+  auto fetch_next = [&]() -> bool {
+    while (true) {
+      if (ft >= t1) return false;
+      while (ft >= fs.tp1 && fs.b + 1 < p.num_seqs) { load_seq<CT>(fs, fs.b + 1, p); blk_base = -1; }
+      const int token0 = fs.start_al + (ft - fs.tp0) * CT + sub * 16;
+      ++ft;
+      if (token0 >= fs.n || token0 + 16 <= fs.start) continue;
+      const int bi = token0 / p.block_size;
+      if (blk_base < 0 || bi < blk_base || bi >= blk_base + 32) {
+        blk_base = bi;
+        const int col = bi + lane;
+        blk_reg = col < p.table_width ? p.block_table[fs.b * p.table_stride + col] : -1;
+      }
+      const int blk = __shfl_sync(FULL, blk_reg, bi - blk_base);
+      int slot0 = -16;                                       // out of range -> TMA zero fill
+      if (blk >= 0 && blk < p.num_blocks) slot0 = blk * p.block_size + (token0 - bi * p.block_size);
+      else if (lane == 0) report(p.dev_status, kDevBadBlock, fs.b);
+      if (lane == 0) {
+        const int st = nfetch % NST;
+        const uint32_t kdst = my_stages + st * C::STAGE_BYTES;
+        mbar_arrive_expect_tx(&bars[st], C::STAGE_BYTES);
+#pragma unroll
+        for (int h = 0; h < C::HALVES; ++h) {
+          asm volatile(
+              "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+              ::"r"(kdst + h * 2048), "l"(reinterpret_cast<uint64_t>(&k_map)), "r"(smem_u32(&bars[st])),
+                "r"(h * 64), "r"(kvh), "r"(slot0) : "memory");
+          asm volatile(
+              "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+              ::"r"(kdst + C::TILE_BYTES + h * 2048), "l"(reinterpret_cast<uint64_t>(&v_map)),
+                "r"(smem_u32(&bars[st])), "r"(h * 64), "r"(kvh), "r"(slot0) : "memory");
+        }
+      }
+      ++nfetch;
+      return true;
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < NST - 1; ++i) fetch_next();
+
+  // ---- consumer side ------------------------------------------------------------------------------
+  SeqView cs;
+  load_seq<CT>(cs, p.first_seq[c], p);
+  const int first_b = cs.b;
+  int t = t0, ncomp = 0;
+  bool dead = false;
+
+  while (t < t1) {
+    while (t >= cs.tp1 && cs.b + 1 < p.num_seqs) load_seq<CT>(cs, cs.b + 1, p);
+    const int seg_end = min(t1, cs.tp1);
+    const bool whole = (t == cs.tp0) && (seg_end == cs.tp1);
+    const int b = cs.b;
+
+    // Q^T as the B operand: lane holds head (lane/4) of the group, dims ks*16 + (lane%4)*2 + {0,1,8,9}
+    uint32_t qf[D / 16][2];
+    {
+      const int g = lane >> 2;
+      const __nv_bfloat16* qrow = p.q + b * p.q_stride + (static_cast<int64_t>(kvh) * G + g) * D + (lane & 3) * 2;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        qf[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16) : 0u;
+        qf[ks][1] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8) : 0u;
+      }
+    }
+    float o[D / 16][4];
+#pragma unroll
+    for (int mt = 0; mt < D / 16; ++mt) { o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f; }
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+    for (; t < seg_end; ++t) {
+      const int token0 = cs.start_al + (t - cs.tp0) * CT + sub * 16;
+      if (token0 >= cs.n || token0 + 16 <= cs.start) continue;
+      if (dead) continue;
+      fetch_next();
+      const int st = ncomp % NST;
+      const uint32_t parity = (ncomp / NST) & 1;
+      const bool ok = mbar_wait(&bars[st], parity);
+      if (!__all_sync(FULL, ok)) {
+        if (lane == 0) report(p.dev_status, kDevWaitTimeout, ncomp);
+        dead = true;
+        continue;
+      }
+      ++ncomp;
+      const uint32_t kbase = my_stages + st * C::STAGE_BYTES;
+      const uint32_t vbase = kbase + C::TILE_BYTES;
+
+      // rows past the end of the sequence may hold anything (even NaN): zero them in V
+      const int valid = cs.n - token0;
+      if (valid < 16) {
+        const int chunks = (16 - valid) * C::HALVES * 8;
+        for (int i = lane; i < chunks; i += 32) {
+          const int r = valid + i / (C::HALVES * 8), rem = i % (C::HALVES * 8);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(vbase + (rem >> 3) * 2048 + r * 128 + (rem & 7) * 16),
+                       "r"(0) : "memory");
+        }
+        __syncwarp();
+      }
+
+      // S^T = K . Q^T
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+        const uint32_t rbase = kbase + row * 128;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const int chunk = ks * 2 + (lane >> 4);
+          uint32_t a[4];
+          ldmatrix_x4(a, rbase + (chunk >> 3) * 2048 + (((chunk & 7) ^ (row & 7)) << 4));
+          if (ks & 1) mma_bf16_16816(s1, a, qf[ks][0], qf[ks][1]);
+          else mma_bf16_16816(s0, a, qf[ks][0], qf[ks][1]);
+        }
+      }
+      const int j0 = token0 + (lane >> 2), j1 = j0 + 8;
+      const bool v0 = j0 < cs.n && j0 >= cs.start, v1 = j1 < cs.n && j1 >= cs.start;
+      const float x0 = v0 ? (s0[0] + s1[0]) * p.scale_log2 : -INFINITY;
+      const float x1 = v0 ? (s0[1] + s1[1]) * p.scale_log2 : -INFINITY;
+      const float x2 = v1 ? (s0[2] + s1[2]) * p.scale_log2 : -INFINITY;
+      const float x3 = v1 ? (s0[3] + s1[3]) * p.scale_log2 : -INFINITY;
+      float ta = fmaxf(x0, x2), tb = fmaxf(x1, x3);
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        ta = fmaxf(ta, __shfl_xor_sync(FULL, ta, off));
+        tb = fmaxf(tb, __shfl_xor_sync(FULL, tb, off));
+      }
+      const float na = fmaxf(m_a, ta), nb = fmaxf(m_b, tb);
+      const float sa = na == -INFINITY ? 0.f : na, sb = nb == -INFINITY ? 0.f : nb;
+      const float alpha_a = fast_exp2(m_a - sa), alpha_b = fast_exp2(m_b - sb);
+      const float p0 = fast_exp2(x0 - sa), p1 = fast_exp2(x1 - sb), p2 = fast_exp2(x2 - sa), p3 = fast_exp2(x3 - sb);
+      l_a = l_a * alpha_a + p0 + p2;
+      l_b = l_b * alpha_b + p1 + p3;
+      m_a = na; m_b = nb;
+      const uint32_t pb0 = movmatrix_trans(pack_bf16(p0, p1));
+      const uint32_t pb1 = movmatrix_trans(pack_bf16(p2, p3));
+
+      // O^T = O^T * alpha + V^T . P^T
+      {
+        const int mi = lane >> 3;
+        const int tok = (lane & 7) + (mi >> 1) * 8;
+        const uint32_t rbase = vbase + tok * 128;
+#pragma unroll
+        for (int mt = 0; mt < D / 16; ++mt) {
+          const int chunk = mt * 2 + (mi & 1);
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, rbase + (chunk >> 3) * 2048 + (((chunk & 7) ^ (tok & 7)) << 4));
+          o[mt][0] *= alpha_a; o[mt][1] *= alpha_b; o[mt][2] *= alpha_a; o[mt][3] *= alpha_b;
+          mma_bf16_16816(o[mt], a, pb0, pb1);
+        }
+      }
+      __syncwarp();
+    }
+
+    // ---- end of segment: merge the warps that share a head, then write output or partial --------
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      l_a += __shfl_xor_sync(FULL, l_a, off);
+      l_b += __shfl_xor_sync(FULL, l_b, off);
+    }
+    {
+      const int ha = (lane & 3) * 2, r = lane >> 2;
+      float* fa = fin + (warp * G + ha) * C::FIN_STRIDE;
+      float* fb = fa + C::FIN_STRIDE;
+      if (ha < G) {
+#pragma unroll
+        for (int mt = 0; mt < D / 16; ++mt) { fa[mt * 16 + r] = o[mt][0]; fa[mt * 16 + r + 8] = o[mt][2]; }
+        if (r == 0) { fa[D] = m_a; fa[D + 1] = l_a; }
+      }
+      if (ha + 1 < G) {
+#pragma unroll
+        for (int mt = 0; mt < D / 16; ++mt) { fb[mt * 16 + r] = o[mt][1]; fb[mt * 16 + r + 8] = o[mt][3]; }
+        if (r == 0) { fb[D] = m_b; fb[D + 1] = l_b; }
+      }
+    }
+    __syncthreads();
+    {
+      const int slot = (b == first_b) ? 0 : 1;
+      for (int e = threadIdx.x; e < HPC * G * D; e += NW * 32) {
+        const int hl = e / (G * D), g = (e / D) % G, dim = e % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int sb = 0; sb < C::TS; ++sb) M = fmaxf(M, fin[((sb * HPC + hl) * G + g) * C::FIN_STRIDE + D]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int sb = 0; sb < C::TS; ++sb) {
+          const float* f = fin + ((sb * HPC + hl) * G + g) * C::FIN_STRIDE;
+          const float w = f[D] == -INFINITY ? 0.f : fast_exp2(f[D] - M);
+          L += f[D + 1] * w;
+          acc += f[dim] * w;
+        }
+        const float val = L > 0.f ? acc / L : 0.f;
+        const int qh = (blockIdx.y * HPC + hl) * G + g;
+        if (whole) {
+          p.out[b * p.out_stride + static_cast<int64_t>(qh) * D + dim] = __float2bfloat16_rn(val);
+        } else {
+          const int64_t pi = (static_cast<int64_t>(c) * 2 + slot) * p.hq + qh;
+          p.part_o[pi * D + dim] = val;
+          if (dim == 0) p.part_lse[pi] = L > 0.f ? M + log2f(L) : -INFINITY;
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // a wait that gave up may leave copies in flight: give them a bounded chance to land
+  if (dead) {
+    for (int i = ncomp; i < nfetch; ++i) mbar_wait(&bars[i % NST], (i / NST) & 1, 1u << 16);
+  }
+}
+
+// ---- combine ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams p, int d) {
+  const int b = blockIdx.x;
+  const int tp0 = p.tile_prefix[b], tp1 = p.tile_prefix[b + 1];
+  const int per = p.hdr->per_cta;
+  const int n_el = p.hq * d;
+  if (tp1 == tp0) {                                          // empty context (graph padding): zeros
+    for (int e = threadIdx.x; e < n_el; e += blockDim.x) p.out[b * p.out_stride + e] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int c1 = tp0 / per, c2 = (tp1 - 1) / per;
+  if (c1 == c2) return;                                      // one CTA held the whole sequence
+  for (int e = threadIdx.x; e < n_el; e += blockDim.x) {
+    const int qh = e / d, dim = e - qh * d;
+    float M = -INFINITY;
+    for (int c = c1; c <= c2; ++c) {
+      const int slot = p.first_seq[c] == b ? 0 : 1;
+      M = fmaxf(M, p.part_lse[(static_cast<int64_t>(c) * 2 + slot) * p.hq + qh]);
+    }
+    float W = 0.f, acc = 0.f;
+    for (int c = c1; c <= c2; ++c) {
+      const int slot = p.first_seq[c] == b ? 0 : 1;
+      const int64_t pi = (static_cast<int64_t>(c) * 2 + slot) * p.hq + qh;
+      const float lse = p.part_lse[pi];
+      const float w = lse == -INFINITY ? 0.f : fast_exp2(lse - M);
+      W += w;
+      acc += w * p.part_o[pi * d + dim];
+    }
+    p.out[b * p.out_stride + e] = __float2bfloat16_rn(W > 0.f ? acc / W : 0.f);
+  }
+}
+
+template <int D, int HPC>
+static int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, const DecodeParams& p, int hkv, int num_ctas,
+                         cudaStream_t stream) {
+  using C = DecodeCfg<D, HPC>;
+  const size_t smem = 1024 + static_cast<size_t>(C::NW) * C::NSTAGES * C::STAGE_BYTES +
+                      C::NW * C::NSTAGES * sizeof(uint64_t) +
+                      static_cast<size_t>(C::NW) * p.group * C::FIN_STRIDE * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(decode_attn_kernel<D, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+        cudaSuccess)
+      return kLaunchFailed;
+    configured = true;
+  }
+  if (smem > 227 * 1024) return kUnsupportedShape;
+  dim3 grid(num_ctas, hkv / HPC);
+  decode_attn_kernel<D, HPC><<<grid, C::NW * 32, smem, stream>>>(km, vm, p);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+}  // namespace mvb
+
+extern "C" size_t mvb_decode_workspace_bytes(int max_seqs, int num_q_heads, int head_dim) {
+  if (max_seqs <= 0 || num_q_heads <= 0 || head_dim <= 0) return 0;
+  return mvb::decode_layout(max_seqs, num_q_heads, head_dim).total;
+}
+
+static int decode_shape_ok(int hq, int hkv, int d) {
+  if (hq <= 0 || hkv <= 0 || hq % hkv != 0) return 0;
+  if (d != 128 && d != 256) return 0;
+  const int g = hq / hkv;
+  if (g > 8) return 0;
+  const int nw = d == 128 ? 8 : 4;
+  if (hkv < nw) return (hkv == 1 || hkv == 2 || hkv == 4);
+  return hkv % nw == 0;
+}
+
+extern "C" int mvb_decode_plan(const int32_t* cache_seqlens, int num_seqs, int window_left, int num_q_heads,
+                               int num_kv_heads, int head_dim, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  using namespace mvb;
+  if (!cache_seqlens || !workspace || num_seqs <= 0) return kInvalidArgument;
+  if (!decode_shape_ok(num_q_heads, num_kv_heads, head_dim)) return kUnsupportedShape;
+  const DecodeLayout l = decode_layout(num_seqs, num_q_heads, head_dim);
+  if (workspace_bytes < l.total || !is_aligned(workspace, 256)) return kInvalidArgument;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int num_ctas = sm_count();
+  if (num_ctas > kMaxCtas) num_ctas = kMaxCtas;
+  decode_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      cache_seqlens, num_seqs, window_left, cta_tokens_for(num_kv_heads, head_dim), num_ctas,
+      reinterpret_cast<DecodeHeader*>(ws), reinterpret_cast<int32_t*>(ws + l.first_seq),
+      reinterpret_cast<int32_t*>(ws + l.tile_prefix));
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+extern "C" int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                               int64_t num_blocks, int block_size, const int32_t* cache_seqlens,
+                               const int32_t* block_table, int64_t table_stride, int table_width, int num_seqs,
+                               int num_q_heads, int num_kv_heads, int head_dim, float scale, int window_left,
+                               void* out, int64_t out_row_stride, void* workspace, size_t workspace_bytes,
+                               int32_t* dev_status, void* stream) {
+  using namespace mvb;
+  if (!q || !k_cache || !v_cache || !cache_seqlens || !block_table || !out || !workspace) return kInvalidArgument;
+  if (num_seqs <= 0 || num_blocks <= 0 || block_size <= 0 || table_width <= 0 || table_stride < table_width)
+    return kInvalidArgument;
+  if (!decode_shape_ok(num_q_heads, num_kv_heads, head_dim)) return kUnsupportedShape;
+  if (block_size % 16 != 0) return kUnsupportedShape;
+  if (num_blocks * block_size > 0x7fffffffLL) return kUnsupportedShape;
+  if ((q_row_stride % 2) || (out_row_stride % 1) || !is_aligned(q, 4) || !is_aligned(out, 2)) return kMisaligned;
+  const DecodeLayout l = decode_layout(num_seqs, num_q_heads, head_dim);
+  if (workspace_bytes < l.total || !is_aligned(workspace, 256)) return kInvalidArgument;
+
+  CUtensorMap km, vm;
+  const int64_t rows = num_blocks * block_size;
+  int rc = make_kv_tensor_map(&km, k_cache, rows, num_kv_heads, head_dim, static_cast<int64_t>(num_kv_heads) * head_dim, 16);
+  if (rc != kOk) return rc;
+  rc = make_kv_tensor_map(&vm, v_cache, rows, num_kv_heads, head_dim, static_cast<int64_t>(num_kv_heads) * head_dim, 16);
+  if (rc != kOk) return rc;
+
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  DecodeParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride = q_row_stride;
+  p.out = static_cast<__nv_bfloat16*>(out); p.out_stride = out_row_stride;
+  p.cache_seqlens = cache_seqlens; p.block_table = block_table; p.table_stride = table_stride;
+  p.table_width = table_width;
+  p.num_seqs = num_seqs; p.hq = num_q_heads; p.group = num_q_heads / num_kv_heads; p.block_size = block_size;
+  p.num_blocks = num_blocks;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window_left = window_left;
+  p.hdr = reinterpret_cast<const DecodeHeader*>(ws);
+  p.first_seq = reinterpret_cast<const int32_t*>(ws + l.first_seq);
+  p.tile_prefix = reinterpret_cast<const int32_t*>(ws + l.tile_prefix);
+  p.part_lse = reinterpret_cast<float*>(ws + l.lse);
+  p.part_o = reinterpret_cast<float*>(ws + l.o);
+  p.dev_status = dev_status;
+
+  int num_ctas = sm_count();
+  if (num_ctas > kMaxCtas) num_ctas = kMaxCtas;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nw = head_dim == 128 ? 8 : 4;
+  const int hpc = num_kv_heads < nw ? num_kv_heads : nw;
+  rc = kUnsupportedShape;
+  if (head_dim == 128) {
+    if (hpc == 8) rc = launch_decode<128, 8>(km, vm, p, num_kv_heads, num_ctas, st);
+    else if (hpc == 4) rc = launch_decode<128, 4>(km, vm, p, num_kv_heads, num_ctas, st);
+    else if (hpc == 2) rc = launch_decode<128, 2>(km, vm, p, num_kv_heads, num_ctas, st);
+    else if (hpc == 1) rc = launch_decode<128, 1>(km, vm, p, num_kv_heads, num_ctas, st);
+  } else {
+    if (hpc == 4) rc = launch_decode<256, 4>(km, vm, p, num_kv_heads, num_ctas, st);
+    else if (hpc == 2) rc = launch_decode<256, 2>(km, vm, p, num_kv_heads, num_ctas, st);
+    else if (hpc == 1) rc = launch_decode<256, 1>(km, vm, p, num_kv_heads, num_ctas, st);
+  }
+  if (rc != kOk) return rc;
+  decode_combine_kernel<<<num_seqs, 256, 0, st>>>(p, head_dim);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}

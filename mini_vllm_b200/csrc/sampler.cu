@@ -1,0 +1,203 @@
+// Fused temperature / top-k / Gumbel-max sampler: one CTA per logits row (HBM-bound:
+// algorithmic bytes = num_rows * vocab * 2; the top-k passes re-read the row from L2).
+//
+// Greedy: argmax of float(logit) / T with the lowest index winning ties, which is what
+// torch.argmax returns on the same fp32 values.
+// Random: radix-select the k-th largest bf16 key with two 256-bin histogram passes, then
+// argmax over the kept entries of  logit / T - log(-log(u)),  u from Philox4x32-10 with
+// counter (column/4, row, offset_lo, offset_hi), key (seed_lo, seed_hi), word column%4.
+#include "common.cuh"
+#include "mini_vllm_b200.h"
+
+namespace mvb {
+
+constexpr int kSampleThreads = 512;
+
+struct Best {
+  float val;
+  int idx;
+};
+
+// NaN counts as the largest value (torch.argmax does the same); lower index wins ties.
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
+  const bool vn = v != v, bn = bv != bv;
+  if (vn || bn) return vn && (!bn || i < bi);
+  return v > bv || (v == bv && i < bi);
+}
+
+__device__ __forceinline__ Best block_argmax(Best b) {
+  __shared__ float sv[kSampleThreads / 32];
+  __shared__ int si[kSampleThreads / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, b.val, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, b.idx, o);
+    if (better(ov, oi, b.val, b.idx)) { b.val = ov; b.idx = oi; }
+  }
+  if (lane == 0) { sv[warp] = b.val; si[warp] = b.idx; }
+  __syncthreads();
+  if (warp == 0) {
+    b.val = lane < kSampleThreads / 32 ? sv[lane] : -INFINITY;
+    b.idx = lane < kSampleThreads / 32 ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, b.val, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, b.idx, o);
+      if (better(ov, oi, b.val, b.idx)) { b.val = ov; b.idx = oi; }
+    }
+  }
+  return b;                                                  // valid in warp 0
+}
+
+// Calls f(column, raw_bf16_bits) for every column of the row; 128-bit loads when the row allows.
+template <class F>
+__device__ __forceinline__ void for_each_logit(const uint16_t* row, int vocab, bool vec_ok, F f) {
+  if (vec_ok) {
+    const int nvec = vocab / 8;
+    for (int v = threadIdx.x; v < nvec; v += kSampleThreads) {
+      const uint4 w = *reinterpret_cast<const uint4*>(row + v * 8);
+      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        f(v * 8 + 2 * i, static_cast<uint16_t>(ws[i] & 0xffffu));
+        f(v * 8 + 2 * i + 1, static_cast<uint16_t>(ws[i] >> 16));
+      }
+    }
+    for (int c = nvec * 8 + threadIdx.x; c < vocab; c += kSampleThreads) f(c, row[c]);
+  } else {
+    for (int c = threadIdx.x; c < vocab; c += kSampleThreads) f(c, row[c]);
+  }
+}
+
+__device__ __forceinline__ float bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+
+// Monotone map bf16 bits -> uint16 (larger float, larger key); -0 and +0 share a key.
+__device__ __forceinline__ uint32_t sort_key(uint16_t b) {
+  if (b == 0x8000u) b = 0;
+  return (b & 0x8000u) ? static_cast<uint32_t>(static_cast<uint16_t>(~b)) : static_cast<uint32_t>(b | 0x8000u);
+}
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                                              uint32_t k1, uint32_t (&out)[4]) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+struct SampleParams {
+  const uint16_t* logits;
+  int64_t row_stride;
+  int vocab;
+  const float* temperatures;
+  const int32_t* top_k;
+  uint64_t seed, offset;
+  int64_t* out;
+};
+
+__global__ void __launch_bounds__(kSampleThreads) sample_greedy_kernel(const SampleParams p) {
+  const int r = blockIdx.x;
+  const uint16_t* row = p.logits + r * p.row_stride;
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
+  const bool scaled = p.temperatures != nullptr;
+  const float temp = scaled ? p.temperatures[r] : 1.f;
+  Best b{-INFINITY, 0x7fffffff};
+  for_each_logit(row, p.vocab, vec_ok, [&](int c, uint16_t bits) {
+    float x = bits_to_float(bits);
+    if (scaled) x = __fdiv_rn(x, temp);
+    if (better(x, c, b.val, b.idx)) { b.val = x; b.idx = c; }
+  });
+  b = block_argmax(b);
+  if (threadIdx.x == 0) p.out[r] = b.idx;
+}
+
+__global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(const SampleParams p) {
+  __shared__ uint32_t hist[256];
+  __shared__ uint32_t sel_s[2];                              // selected bin, entries needed inside it
+  const int r = blockIdx.x;
+  const uint16_t* row = p.logits + r * p.row_stride;
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
+  const float temp = p.temperatures != nullptr ? p.temperatures[r] : 1.f;
+  const bool scaled = p.temperatures != nullptr;
+  const int k = p.top_k[r];
+
+  uint32_t thresh = 0;                                       // keep keys >= thresh
+  if (k > 0 && k < p.vocab) {
+    // pass 1: high byte
+    for (int i = threadIdx.x; i < 256; i += kSampleThreads) hist[i] = 0;
+    __syncthreads();
+    for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) { atomicAdd(&hist[sort_key(bits) >> 8], 1u); });
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t need = k, bin = 0;
+      for (int i = 255; i >= 0; --i) {
+        if (hist[i] >= need) { bin = i; break; }
+        need -= hist[i];
+      }
+      sel_s[0] = bin; sel_s[1] = need;
+    }
+    __syncthreads();
+    const uint32_t hi_bin = sel_s[0], need_hi = sel_s[1];
+    __syncthreads();
+    // pass 2: low byte inside the selected high bin
+    for (int i = threadIdx.x; i < 256; i += kSampleThreads) hist[i] = 0;
+    __syncthreads();
+    for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) {
+      const uint32_t key = sort_key(bits);
+      if ((key >> 8) == hi_bin) atomicAdd(&hist[key & 0xffu], 1u);
+    });
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t need = need_hi, bin = 0;
+      for (int i = 255; i >= 0; --i) {
+        if (hist[i] >= need) { bin = i; break; }
+        need -= hist[i];
+      }
+      sel_s[0] = bin;
+    }
+    __syncthreads();
+    thresh = (hi_bin << 8) | sel_s[0];
+  }
+
+  const uint32_t k0 = static_cast<uint32_t>(p.seed), k1 = static_cast<uint32_t>(p.seed >> 32);
+  const uint32_t o0 = static_cast<uint32_t>(p.offset), o1 = static_cast<uint32_t>(p.offset >> 32);
+  Best b{-INFINITY, 0x7fffffff};
+  uint32_t rnd[4];
+  int rnd_group = -1;
+  for_each_logit(row, p.vocab, vec_ok, [&](int c, uint16_t bits) {
+    if (sort_key(bits) < thresh) return;
+    if ((c >> 2) != rnd_group) {
+      rnd_group = c >> 2;
+      philox4x32_10(static_cast<uint32_t>(rnd_group), static_cast<uint32_t>(r), o0, o1, k0, k1, rnd);
+    }
+    const float u = __fmul_rn(__fadd_rn(static_cast<float>(rnd[c & 3] >> 9), 0.5f), 1.0f / 8388608.0f);
+    float x = bits_to_float(bits);
+    if (scaled) x = __fdiv_rn(x, temp);
+    const float score = __fsub_rn(x, logf(-logf(u)));
+    if (better(score, c, b.val, b.idx)) { b.val = score; b.idx = c; }
+  });
+  b = block_argmax(b);
+  if (threadIdx.x == 0) p.out[r] = b.idx;
+}
+
+}  // namespace mvb
+
+extern "C" int mvb_sample(const void* logits, int64_t row_stride, int num_rows, int vocab,
+                          const float* temperatures, const int32_t* top_k, uint64_t seed, uint64_t offset,
+                          int64_t* out, int32_t* dev_status, void* stream) {
+  using namespace mvb;
+  (void)dev_status;
+  if (!logits || !out || num_rows < 0 || vocab <= 0 || row_stride < vocab) return kInvalidArgument;
+  if (num_rows == 0) return kOk;
+  SampleParams p{static_cast<const uint16_t*>(logits), row_stride, vocab, temperatures, top_k, seed, offset, out};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (top_k == nullptr) sample_greedy_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);
+  else sample_topk_gumbel_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}

@@ -1,0 +1,220 @@
+"""Tensor-level wrappers over the C ABI: pointers, strides and the current CUDA stream.
+
+Each function validates shapes/dtypes, passes raw device pointers to the library and
+raises on a non-zero status.  Nothing here computes on the host.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+
+_DEV_ERRORS = {1: "slot outside the KV pool", 2: "block id outside the KV pool",
+               3: "position outside the cos/sin table", 4: "a bounded device wait ran out",
+               5: "sequence length does not fit its block list"}
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, dtype, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (the kernels have no CPU path)")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _heads_contiguous(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 3 or t.stride(2) != 1 or t.stride(1) != t.shape[2]:
+        raise ValueError(f"{name} must be [tokens, heads, head_dim] with contiguous heads")
+
+
+def new_status(device) -> torch.Tensor:
+    """A zeroed device int32[4] for kernels to record device-detected errors in."""
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor) -> None:
+    """Synchronising read of a status word; raises if a kernel recorded an error."""
+    code, detail, block, thread = status.tolist()
+    if code:
+        raise _cabi.KernelError(f"device error {code} ({_DEV_ERRORS.get(code, '?')}), detail {detail}, "
+                                f"block {block}, thread {thread}")
+
+
+def pack_prefill(meta: torch.Tensor, num_seqs: int, num_tokens: int, num_blocks_total: int, table_width: int,
+                 block_size: int, want_table: bool, status: torch.Tensor | None = None) -> dict:
+    """meta: device int32 = [seq_len(B) | cached_len(B) | blk_off(B+1) | blocks_flat | new_tokens(T)]."""
+    _need(meta, torch.int32, "meta")
+    dev = meta.device
+    B, T = num_seqs, num_tokens
+    base, es = meta.data_ptr(), 4
+    o_seq, o_cached, o_off = 0, B, 2 * B
+    o_blocks = o_off + B + 1
+    o_tok = o_blocks + num_blocks_total
+    assert meta.numel() >= o_tok + T
+    out = {
+        "input_ids": torch.empty(T, dtype=torch.int64, device=dev),
+        "positions": torch.empty(T, dtype=torch.int64, device=dev),
+        "slot_mapping": torch.empty(T, dtype=torch.int32, device=dev),
+        "cu_seqlens_q": torch.empty(B + 1, dtype=torch.int32, device=dev),
+        "cu_seqlens_k": torch.empty(B + 1, dtype=torch.int32, device=dev),
+        "block_table": torch.empty(B, table_width, dtype=torch.int32, device=dev) if want_table else None,
+    }
+    rc = _cabi.load().mvb_pack_prefill(
+        base + es * o_seq, base + es * o_cached, base + es * o_off, base + es * o_blocks, base + es * o_tok,
+        B, T, table_width, block_size, _ptr(out["input_ids"]), _ptr(out["positions"]), _ptr(out["slot_mapping"]),
+        _ptr(out["cu_seqlens_q"]), _ptr(out["cu_seqlens_k"]), _ptr(out["block_table"]), _ptr(status), _stream())
+    _cabi.check(rc, "mvb_pack_prefill")
+    return out
+
+
+def pack_decode(meta: torch.Tensor, num_seqs: int, num_blocks_total: int, table_width: int, block_size: int,
+                input_ids: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor,
+                cache_seqlens: torch.Tensor, block_table: torch.Tensor, padded_seqs: int | None = None,
+                prev_sampled: torch.Tensor | None = None, status: torch.Tensor | None = None) -> None:
+    """meta: device int32 = [seq_len(B) | blk_off(B+1) | blocks_flat | host_tokens(B) | src_index(B)].
+
+    Outputs are written into the given (possibly static, graph-owned) buffers; rows
+    ``num_seqs..padded_seqs-1`` become padding rows.
+    """
+    _need(meta, torch.int32, "meta")
+    B = num_seqs
+    padded = B if padded_seqs is None else padded_seqs
+    base, es = meta.data_ptr(), 4
+    o_off = B
+    o_blocks = o_off + B + 1
+    o_tok = o_blocks + num_blocks_total
+    o_src = o_tok + B
+    assert meta.numel() >= o_src + B
+    assert block_table.dim() == 2 and block_table.stride(1) == 1 and block_table.shape[1] >= table_width
+    for t, n in ((input_ids, "input_ids"), (positions, "positions")):
+        _need(t, torch.int64, n)
+        assert t.numel() >= padded and t.is_contiguous()
+    for t, n in ((slot_mapping, "slot_mapping"), (cache_seqlens, "cache_seqlens"), (block_table, "block_table")):
+        _need(t, torch.int32, n)
+    assert block_table.shape[0] >= padded
+    rc = _cabi.load().mvb_pack_decode(
+        base, base + es * o_off, base + es * o_blocks, base + es * o_tok, _ptr(prev_sampled),
+        base + es * o_src if prev_sampled is not None else None, B, padded, table_width, block_table.stride(0),
+        block_size, _ptr(input_ids), _ptr(positions), _ptr(slot_mapping), _ptr(cache_seqlens), _ptr(block_table),
+        _ptr(status), _stream())
+    _cabi.check(rc, "mvb_pack_decode")
+
+
+def rope_kv_write(q: torch.Tensor | None, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor | None,
+                  cos_sin: torch.Tensor | None, slot_mapping: torch.Tensor | None,
+                  k_cache: torch.Tensor | None, v_cache: torch.Tensor | None, k_in_place: bool = True,
+                  status: torch.Tensor | None = None) -> None:
+    """Rotate q (in place) and k, write k/v to their cache slots.  cos_sin=None: no rotation."""
+    _need(k, torch.bfloat16, "k"); _need(v, torch.bfloat16, "v")
+    _heads_contiguous(k, "k"); _heads_contiguous(v, "v")
+    T, hkv, d = k.shape
+    hq = 0
+    if q is not None:
+        _need(q, torch.bfloat16, "q"); _heads_contiguous(q, "q")
+        assert q.shape[0] == T and q.shape[2] == d
+        hq = q.shape[1]
+    max_pos = 0
+    if cos_sin is not None:
+        _need(cos_sin, torch.float32, "cos_sin"); _need(positions, torch.int64, "positions")
+        assert cos_sin.is_contiguous() and cos_sin.shape[1] == d and positions.numel() == T
+        max_pos = cos_sin.shape[0]
+    num_slots = 0
+    if slot_mapping is not None:
+        _need(slot_mapping, torch.int32, "slot_mapping")
+        assert slot_mapping.numel() == T
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape[-2:] == (hkv, d)
+        num_slots = k_cache.shape[0] * k_cache.shape[1]
+    rc = _cabi.load().mvb_rope_kv_write(
+        _ptr(q), q.stride(0) if q is not None else 0, _ptr(k), k.stride(0), _ptr(v), v.stride(0),
+        _ptr(positions) if cos_sin is not None else None, _ptr(cos_sin), max_pos, _ptr(slot_mapping),
+        _ptr(k_cache) if slot_mapping is not None else None, _ptr(v_cache) if slot_mapping is not None else None,
+        num_slots, T, hq, hkv, d, 1 if k_in_place else 0, _ptr(status), _stream())
+    _cabi.check(rc, "mvb_rope_kv_write")
+
+
+def decode_workspace(max_seqs: int, num_q_heads: int, head_dim: int, device) -> torch.Tensor:
+    n = _cabi.load().mvb_decode_workspace_bytes(max_seqs, num_q_heads, head_dim)
+    if n == 0:
+        raise ValueError("bad decode workspace shape")
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
+def decode_plan(cache_seqlens: torch.Tensor, window_left: int, num_q_heads: int, num_kv_heads: int,
+                head_dim: int, workspace: torch.Tensor) -> None:
+    _need(cache_seqlens, torch.int32, "cache_seqlens")
+    rc = _cabi.load().mvb_decode_plan(_ptr(cache_seqlens), cache_seqlens.numel(), window_left, num_q_heads,
+                                      num_kv_heads, head_dim, _ptr(workspace), workspace.numel(), _stream())
+    _cabi.check(rc, "mvb_decode_plan")
+
+
+def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_seqlens: torch.Tensor,
+                block_table: torch.Tensor, scale: float, window_left: int, workspace: torch.Tensor,
+                out: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """q [B,Hq,D]; the plan for (cache_seqlens, window_left) must already be in ``workspace``."""
+    _need(q, torch.bfloat16, "q"); _heads_contiguous(q, "q")
+    _need(cache_seqlens, torch.int32, "cache_seqlens"); _need(block_table, torch.int32, "block_table")
+    B, hq, d = q.shape
+    nblk, bs, hkv, d2 = k_cache.shape
+    assert d2 == d and k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.shape == k_cache.shape
+    assert block_table.dim() == 2 and block_table.stride(1) == 1 and block_table.shape[0] >= B
+    assert cache_seqlens.numel() >= B
+    if out is None:
+        out = torch.empty(B, hq, d, dtype=torch.bfloat16, device=q.device)
+    rc = _cabi.load().mvb_decode_attn(
+        _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), nblk, bs, _ptr(cache_seqlens), _ptr(block_table),
+        block_table.stride(0), block_table.shape[1], B, hq, hkv, d, float(scale), window_left, _ptr(out),
+        out.stride(0), _ptr(workspace), workspace.numel(), _ptr(status), _stream())
+    _cabi.check(rc, "mvb_decode_attn")
+    return out
+
+
+def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
+                 cu_seqlens_k: torch.Tensor, max_seqlen_q: int, scale: float, window_left: int = -1,
+                 block_table: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                 status: torch.Tensor | None = None) -> torch.Tensor:
+    """q [Tq,Hq,D]; k/v dense [Tk,Hkv,D] (block_table None) or the paged pool [blocks,bs,Hkv,D]."""
+    _need(q, torch.bfloat16, "q"); _heads_contiguous(q, "q")
+    _need(cu_seqlens_q, torch.int32, "cu_seqlens_q"); _need(cu_seqlens_k, torch.int32, "cu_seqlens_k")
+    Tq, hq, d = q.shape
+    if block_table is None:
+        _heads_contiguous(k, "k"); _heads_contiguous(v, "v")
+        assert k.stride(0) == v.stride(0), "k and v must share a row stride"
+        kv_rows, hkv, kv_stride, bs, tstride = k.shape[0], k.shape[1], k.stride(0), 0, 0
+    else:
+        _need(block_table, torch.int32, "block_table")
+        assert k.dim() == 4 and k.is_contiguous() and v.is_contiguous()
+        nblk, bs, hkv, _ = k.shape
+        kv_rows, kv_stride, tstride = nblk * bs, hkv * d, block_table.stride(0)
+    if out is None:
+        out = torch.empty(Tq, hq, d, dtype=torch.bfloat16, device=q.device)
+    rc = _cabi.load().mvb_prefill_attn(
+        _ptr(q), q.stride(0), _ptr(k), _ptr(v), kv_stride, kv_rows, _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
+        _ptr(block_table), tstride, bs, cu_seqlens_q.numel() - 1, Tq, int(max_seqlen_q), hq, hkv, d, float(scale),
+        window_left, _ptr(out), out.stride(0), _ptr(status), _stream())
+    _cabi.check(rc, "mvb_prefill_attn")
+    return out
+
+
+def sample(logits: torch.Tensor, temperatures: torch.Tensor | None = None, top_k: torch.Tensor | None = None,
+           seed: int = 0, offset: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """logits bf16 [B,V] -> int64 [B].  top_k None: greedy; else temperature/top-k/Gumbel-max."""
+    _need(logits, torch.bfloat16, "logits")
+    assert logits.dim() == 2 and logits.stride(1) == 1
+    B, V = logits.shape
+    if temperatures is not None:
+        _need(temperatures, torch.float32, "temperatures")
+    if top_k is not None:
+        _need(top_k, torch.int32, "top_k")
+    if out is None:
+        out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    rc = _cabi.load().mvb_sample(_ptr(logits), logits.stride(0), B, V, _ptr(temperatures), _ptr(top_k),
+                                 seed & (2**64 - 1), offset & (2**64 - 1), _ptr(out), None, _stream())
+    _cabi.check(rc, "mvb_sample")
+    return out

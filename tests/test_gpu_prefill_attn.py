@@ -1,0 +1,114 @@
+"""Varlen causal prefill attention (tcgen05, through the C ABI) against the fp32 oracle."""
+import pytest
+import torch
+
+from mini_vllm_b200 import ops
+from mini_vllm_b200.workloads import BLOCK_SIZE, cdiv, config1, config3, generator, randn_bf16
+from oracle import attention as oattn
+from tests.helpers import assert_close_attn, fill_paged, sequential_tables, table_tensor
+
+pytestmark = pytest.mark.gpu
+
+
+def cu(lens):
+    return torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32)
+
+
+def run_dense(cuda, lens, hq, hkv, d, window_left=-1, seed=0, packed_qkv=False):
+    g = generator(seed)
+    T = sum(lens)
+    if packed_qkv:                     # q/k/v are column slices of one GEMM output, as in the Qwen3 layer
+        qkv = randn_bf16(g, T, (hq + 2 * hkv) * d)
+        q, k, v = (t.view(T, -1, d) for t in qkv.split([hq * d, hkv * d, hkv * d], dim=-1))
+        qkv_d = qkv.to(cuda)
+        qd, kd, vd = (t.view(T, -1, d) for t in qkv_d.split([hq * d, hkv * d, hkv * d], dim=-1))
+    else:
+        q, k, v = randn_bf16(g, T, hq, d), randn_bf16(g, T, hkv, d), randn_bf16(g, T, hkv, d)
+        qd, kd, vd = q.to(cuda), k.to(cuda), v.to(cuda)
+    cq = cu(lens)
+    want = oattn.prefill(q, k, v, cq, cq, window_left=window_left)
+    status = ops.new_status(cuda)
+    out = ops.prefill_attn(qd, kd, vd, cq.to(cuda), cq.to(cuda), max(lens), d ** -0.5, window_left, status=status)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    assert_close_attn(out, want, f"prefill dense lens={lens[:4]}.. hq={hq} hkv={hkv} d={d} w={window_left}")
+
+
+def run_paged(cuda, q_lens, k_lens, hq, hkv, d, window_left=-1, seed=0, tables=None, num_blocks=None, g=None):
+    g = g or generator(seed)
+    num_blocks = num_blocks or sum(cdiv(n, BLOCK_SIZE) for n in k_lens) + 2
+    tables = tables or sequential_tables(g, k_lens, num_blocks)
+    k_pool, v_pool = fill_paged(g, k_lens, tables, num_blocks, hkv, d)
+    q = randn_bf16(g, sum(q_lens), hq, d)
+    cq, ck, bt = cu(q_lens), cu(k_lens), table_tensor(tables)
+    want = oattn.prefill(q, k_pool, v_pool, cq, ck, block_table=bt, window_left=window_left)
+    status = ops.new_status(cuda)
+    out = ops.prefill_attn(q.to(cuda), k_pool.to(cuda), v_pool.to(cuda), cq.to(cuda), ck.to(cuda), max(q_lens),
+                           d ** -0.5, window_left, block_table=bt.to(cuda), status=status)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    assert_close_attn(out, want, f"prefill paged q={q_lens[:4]}.. k={k_lens[:4]}.. d={d} w={window_left}")
+
+
+def test_single_short_sequence(cuda):
+    run_dense(cuda, [37], 16, 8, 128)
+
+
+def test_tile_boundary_lengths(cuda):
+    run_dense(cuda, [1, 127, 128, 129, 255, 256, 257, 300], 16, 8, 128, seed=1)
+
+
+def test_config1_prefill_packed_qkv(cuda):
+    case, _ = config1()
+    run_dense(cuda, case.prefill_lens, 16, 8, 128, seed=2, packed_qkv=True)
+
+
+def test_long_sequence(cuda):
+    run_dense(cuda, [2048, 700], 16, 8, 128, seed=3)
+
+
+@pytest.mark.parametrize("hq,hkv", [(4, 4), (8, 2), (8, 1), (32, 8)])
+def test_gqa_ratios(cuda, hq, hkv):
+    run_dense(cuda, [200, 513], hq, hkv, 128, seed=hq + hkv)
+
+
+def test_head_dim_256(cuda):
+    run_dense(cuda, [64, 300, 129], 4, 1, 256, seed=4)
+
+
+@pytest.mark.parametrize("window", [0, 64, 512])
+def test_sliding_window(cuda, window):
+    run_dense(cuda, [100, 700, 1300], 4, 1, 256, window_left=window, seed=5)
+    run_dense(cuda, [100, 700], 16, 8, 128, window_left=window, seed=6)
+
+
+def test_paged_full_prefill_matches_dense_semantics(cuda):
+    run_paged(cuda, [244, 460, 485], [244, 460, 485], 16, 8, 128, seed=7)
+
+
+def test_paged_prefix_cached_suffix_queries(cuda):
+    """q_len < k_len: queries cover only the suffix, bottom-right aligned causal mask."""
+    run_paged(cuda, [100, 1, 300, 257], [612, 513, 812, 257], 16, 8, 128, seed=8)
+
+
+def test_paged_shared_prefix_blocks(cuda):
+    """Two sequences share their first two blocks (same-step prefix sharing)."""
+    g = generator(9)
+    tables = [[5, 6, 1], [5, 6, 2, 3], [7]]
+    k_lens, q_lens = [700, 1000, 90], [188, 488, 90]
+    # build pools so that the shared blocks hold the same keys for both sequences
+    k_pool, v_pool = fill_paged(g, [1000, 700 - 512, 90], [[5, 6, 2, 3], [1], [7]], 8, 8, 128)
+    q = randn_bf16(g, sum(q_lens), 16, 128)
+    cq, ck, bt = cu(q_lens), cu(k_lens), table_tensor(tables)
+    want = oattn.prefill(q, k_pool, v_pool, cq, ck, block_table=bt)
+    out = ops.prefill_attn(q.to(cuda), k_pool.to(cuda), v_pool.to(cuda), cq.to(cuda), ck.to(cuda), max(q_lens),
+                           128 ** -0.5, -1, block_table=bt.to(cuda))
+    torch.cuda.synchronize()
+    assert_close_attn(out, want, "shared prefix")
+
+
+def test_config3_prefill_part(cuda):
+    case, g = config3()
+    q_lens = [n - c for n, c in zip(case.prefill_lens, case.prefill_cached)]
+    run_paged(cuda, q_lens, case.prefill_lens, 16, 8, 128, tables=case.prefill_blocks,
+              num_blocks=case.pool_blocks, g=g)

@@ -1,0 +1,68 @@
+"""Sampler kernel (CUDA) against torch.argmax (greedy, bit-exact) and the Philox/Gumbel oracle."""
+import pytest
+import torch
+
+from mini_vllm_b200 import ops
+from mini_vllm_b200.workloads import generator, randn_bf16
+from oracle import sampler as osamp
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,V", [(1, 151936), (64, 151936), (7, 262144), (5, 1000), (3, 1003)])
+def test_greedy_is_first_argmax(cuda, B, V):
+    g = generator(B + V)
+    logits = randn_bf16(g, B, V) * 4
+    logits[0, 17] = logits[0].max()          # force ties: the lowest index must win
+    logits[0, 5] = logits[0].max()
+    out = ops.sample(logits.to(cuda))
+    assert out.dtype == torch.int64
+    assert torch.equal(out.cpu(), osamp.greedy(logits))
+
+
+def test_greedy_with_temperature_and_row_stride(cuda):
+    g = generator(5)
+    full = randn_bf16(g, 6, 4096 + 8)
+    logits = full[:, 8:]                      # rows start 16 bytes in, stride != vocab
+    temps = torch.tensor([0.5, 1.0, 2.0, 0.1, 3.3, 0.7])
+    out = ops.sample(full.to(cuda)[:, 8:], temperatures=temps.to(cuda))
+    assert torch.equal(out.cpu(), osamp.greedy(logits, temps))
+
+
+@pytest.mark.parametrize("V", [1000, 151936])
+def test_topk_gumbel_matches_oracle(cuda, V):
+    g = generator(9)
+    B = 12
+    logits = randn_bf16(g, B, V) * 3
+    temps = torch.tensor([0.7, 1.0, 1.3] * 4)
+    top_k = torch.tensor([1, 2, 5, 50, 0, 1000, 3, 8, 1, 40, V, 7], dtype=torch.int32)
+    seed, offset = 1234567890123, 42
+    out = ops.sample(logits.to(cuda), temps.to(cuda), top_k.to(cuda), seed, offset).cpu()
+    scores = osamp.gumbel_scores(logits, temps, top_k, seed, offset)
+    best = scores.max(dim=-1).values
+    picked = scores[torch.arange(B), out]
+    # device logf may differ from the host's in the last ulp: the pick must be (one of) the best
+    assert torch.isfinite(picked).all(), "picked a token outside the top-k set"
+    assert (best - picked).abs().max().item() <= 1e-4
+    assert (out == scores.argmax(-1)).float().mean().item() >= 0.9
+    # top_k = 1 rows are greedy whatever the noise
+    greedy = osamp.greedy(logits)
+    assert out[0] == greedy[0] and out[8] == greedy[8]
+    # a different offset gives a different stream somewhere
+    out2 = ops.sample(logits.to(cuda), temps.to(cuda), top_k.to(cuda), seed, offset + 1).cpu()
+    assert not torch.equal(out, out2)
+
+
+def test_topk_frequencies_follow_softmax(cuda):
+    """Gumbel-max draws follow softmax(logits / T) restricted to the top-k set."""
+    V, k, n = 64, 4, 4000
+    g = generator(21)
+    row = randn_bf16(g, 1, V)
+    logits = row.expand(n, V).contiguous()
+    temps = torch.full((n,), 0.8)
+    out = ops.sample(logits.to(cuda), temps.to(cuda), torch.full((n,), k, dtype=torch.int32).to(cuda), 77, 0).cpu()
+    top = torch.topk(row[0].float(), k)
+    probs = torch.softmax(top.values / 0.8, -1)
+    counts = torch.stack([(out == i).sum() for i in top.indices]).float() / n
+    assert counts.sum().item() == pytest.approx(1.0)
+    assert (counts - probs).abs().max().item() < 0.04
