@@ -1,0 +1,384 @@
+#!/usr/bin/env python
+"""Benchmark of the ragged continuous-batching attention path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (``config.workload``): Qwen3-0.6B-shape random-init model, 64 requests per GPU with random
+token-id prompts, prompt lengths U[100,1024], output lengths U[100,1024] capped so prompt+output
+<= 1024, continuous batching, greedy decoding.  One "step" is one complete generation job over
+that request set.  At N > 1 each rank is an independent engine replica (no collective on the data
+path); the global request list of 64*N requests is partitioned by the host dispatcher by token
+count, so per-GPU work is fixed: weak scaling.
+
+Metric: prompt+generated tokens per second, whole job, all GPUs.
+* ``value``: the job timed with CUDA events.
+* ``e2e``: the same job through ``Engine.generate`` with host token lists in and out (wall clock,
+  uploads and result reads inside the timed region).
+* ``roofline``: decode attention kernel, the largest kernel of the step: K/V bytes of the contexts
+  it read / CUDA-event time, replayed on contexts recorded during the job, against the measured
+  HBM copy bandwidth.  ``kernels`` adds the same figure on the fixed 240-sequence decode batch
+  (contexts U[128,4096]) and the prefill kernel's TFLOP/s.
+* ``cpu_baseline`` / ``--impl reference``: the oracle restatement of the reference's PyTorch path
+  timed on the host cores on a bounded sample of the same workload (per-token extrapolation).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from mini_vllm_b200.config import Config, SamplingParams, qwen3_shape  # noqa: E402
+from mini_vllm_b200.workloads import (QWEN3_0P6B, config2_requests, config3, decode_kv_bytes,  # noqa: E402
+                                       prefill_flops)
+
+METRIC = "ragged prefill+decode tokens/s (Qwen3-0.6B shapes, 64 requests per GPU, greedy)"
+WORKLOAD = "config2: Qwen3-0.6B random-init, 64 req/GPU, prompt U[100,1024], total<=1024, continuous batching"
+
+
+def measured_peaks() -> tuple[dict, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return json.loads(p.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def partition_by_tokens(requests, n_parts: int):
+    """Host dispatcher: longest first, each request to the replica with the fewest tokens so far."""
+    order = sorted(range(len(requests)), key=lambda i: -(len(requests[i].prompt) + requests[i].max_tokens))
+    loads, parts = [0] * n_parts, [[] for _ in range(n_parts)]
+    for i in order:
+        j = min(range(n_parts), key=lambda r: (loads[r], r))
+        parts[j].append(i)
+        loads[j] += len(requests[i].prompt) + requests[i].max_tokens
+    return [sorted(p) for p in parts]
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc = gpu_index, None
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [r.split(", ") for r in Path(self.file.name).read_text().strip().splitlines() if r.count(",") >= 8]
+        os.unlink(self.file.name)
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [float(r[1]) for r in rows]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in rows for n, v in zip(names, r[5:9]) if v.strip().lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][2]), "samples": len(rows),
+                "power_w_max": max(float(r[3]) for r in rows), "reasons": reasons}
+
+
+# ---------------------------------------------------------------------------------------------------
+def build_engine(local_rank: int):
+    from mini_vllm_b200.engine.engine import Engine
+    torch.cuda.set_device(local_rank)
+    cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=512, max_num_batched_seqs=64,
+                 max_num_batched_tokens=16384, gpu_memory_utilization=0.5, use_cuda_graph=True, seed=0)
+    return Engine(cfg)
+
+
+def run_job(engine, reqs, record_contexts=None):
+    """One generation job through the public API; returns (tokens processed, wall seconds, cuda ms)."""
+    prompts = [r.prompt for r in reqs]
+    params = [SamplingParams(max_tokens=r.max_tokens, ignore_eos=True) for r in reqs]
+    ex = engine.executor
+    if record_contexts is not None:
+        orig = ex._build_decode_input
+        count = [0]
+
+        def spy(requests):
+            if count[0] % 40 == 20:
+                record_contexts.append(([len(r.tokens) for r in requests], [list(r.blocks) for r in requests]))
+            count[0] += 1
+            return orig(requests)
+        ex._build_decode_input = spy
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    out = engine.generate(prompts, params, use_tqdm=False)
+    e1.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    if record_contexts is not None:
+        ex._build_decode_input = orig
+    n_tok = sum(len(p) for p in prompts) + sum(len(o["tokens"]) for o in out)
+    assert all(len(o["tokens"]) == r.max_tokens for o, r in zip(out, reqs))
+    return n_tok, wall, e0.elapsed_time(e1)
+
+
+def decode_roofline(engine, contexts, peaks):
+    """Replay the decode-attention kernel on recorded step contexts over the engine's own KV pool."""
+    from mini_vllm_b200 import ops
+    from mini_vllm_b200.workloads import table_tensor
+    ex = engine.executor
+    dev, hf = ex.device, engine.config.hf_config
+    hq, hkv, d, layers = hf.num_attention_heads, hf.num_key_value_heads, hf.head_dim, hf.num_hidden_layers
+    total_bytes = total_ms = 0.0
+    launches = 0
+    for lens, blocks in contexts:
+        b = len(lens)
+        q = torch.randn(b, hq, d, device=dev, dtype=torch.bfloat16)
+        seqlens = torch.tensor(lens, dtype=torch.int32, device=dev)
+        bt = table_tensor(blocks).to(dev)
+        ws = ops.decode_workspace(b, hq, d, dev)
+        out = torch.empty_like(q)
+        ops.decode_plan(seqlens, -1, hq, hkv, d, ws)
+        for layer in range(3):                                   # warm-up launches
+            ops.decode_attn(q, ex.kv_cache[0, layer], ex.kv_cache[1, layer], seqlens, bt, d ** -0.5, -1, ws, out=out)
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(layers + 1)]
+        evs[0].record()
+        for layer in range(layers):                              # distinct layer pools: no L2 reuse between launches
+            ops.decode_attn(q, ex.kv_cache[0, layer], ex.kv_cache[1, layer], seqlens, bt, d ** -0.5, -1, ws, out=out)
+            evs[layer + 1].record()
+        torch.cuda.synchronize()
+        total_ms += sum(evs[i].elapsed_time(evs[i + 1]) for i in range(layers))
+        total_bytes += layers * decode_kv_bytes(QWEN3_0P6B, lens)
+        launches += layers
+    achieved = total_bytes / (total_ms * 1e-3) / 1e9 if total_ms else 0.0
+    return {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None, "kernel": "decode_attn_kernel<128,8>",
+            "launches_timed": launches, "avg_launch_us": round(total_ms * 1e3 / max(launches, 1), 2),
+            "avg_bytes_per_launch": int(total_bytes / max(launches, 1)),
+            "note": "algorithmic K+V bytes of recorded decode steps (incl. combine kernel time); peak = STREAM copy"}
+
+
+def kernel_extras(dev, peaks):
+    """Fixed single-layer cases: the 240-sequence decode batch and the 16-sequence prefill batch."""
+    from mini_vllm_b200 import ops
+    from mini_vllm_b200.workloads import table_tensor
+    case, _ = config3()
+    hq, hkv, d, nl = 16, 8, 128, 4
+    pools = [torch.randn(2, case.pool_blocks, 256, hkv, d, device=dev, dtype=torch.bfloat16) for _ in range(nl)]
+    out = {}
+    # decode part
+    b = len(case.decode_ctx)
+    q = torch.randn(b, hq, d, device=dev, dtype=torch.bfloat16)
+    lens = torch.tensor(case.decode_ctx, dtype=torch.int32, device=dev)
+    bt = table_tensor(case.decode_blocks).to(dev)
+    ws = ops.decode_workspace(b, hq, d, dev)
+    o = torch.empty_like(q)
+    ops.decode_plan(lens, -1, hq, hkv, d, ws)
+    iters = 24
+    for i in range(8):
+        ops.decode_attn(q, pools[i % nl][0], pools[i % nl][1], lens, bt, d ** -0.5, -1, ws, out=o)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+    evs[0].record()
+    for i in range(iters):
+        ops.decode_attn(q, pools[i % nl][0], pools[i % nl][1], lens, bt, d ** -0.5, -1, ws, out=o)
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    ms = statistics.median(evs[i].elapsed_time(evs[i + 1]) for i in range(iters))
+    byts = decode_kv_bytes(QWEN3_0P6B, case.decode_ctx)
+    gbs = byts / ms / 1e6
+    out["decode_attn_config3"] = {"GB/s": round(gbs, 1), "us": round(ms * 1e3, 1), "bytes": byts,
+                                  "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                                  "frac_of_8TBs_nominal": round(gbs / 8000.0, 4)}
+    # prefill part (paged, half the sequences with a cached 512-token prefix)
+    q_lens = [n - c for n, c in zip(case.prefill_lens, case.prefill_cached)]
+    tq = sum(q_lens)
+    cu = lambda xs: torch.tensor([0] + list(torch.tensor(xs).cumsum(0)), dtype=torch.int32, device=dev)
+    qp = torch.randn(tq, hq, d, device=dev, dtype=torch.bfloat16)
+    btp = table_tensor(case.prefill_blocks).to(dev)
+    cq, ck = cu(q_lens), cu(case.prefill_lens)
+    for i in range(3):
+        ops.prefill_attn(qp, pools[0][0], pools[0][1], cq, ck, max(q_lens), d ** -0.5, -1, block_table=btp)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(11)]
+    evs[0].record()
+    for i in range(10):
+        ops.prefill_attn(qp, pools[i % nl][0], pools[i % nl][1], cq, ck, max(q_lens), d ** -0.5, -1, block_table=btp)
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    ms = statistics.median(evs[i].elapsed_time(evs[i + 1]) for i in range(10))
+    fl = prefill_flops(QWEN3_0P6B, case.prefill_lens, case.prefill_cached)
+    tf = fl / ms / 1e9
+    out["prefill_attn_config3"] = {"TFLOP/s": round(tf, 1), "us": round(ms * 1e3, 1), "flops": fl,
+                                   "frac_of_measured_bf16": round(tf / peaks["bf16_tflops"], 4)}
+    return out
+
+
+# ---- CPU leg: the oracle restatement of the reference path on the host cores ------------------------
+def cpu_reference_sample(budget_s: float = 20.0, seed: int = 0):
+    """Prefill + decode of a few config-2 requests through the oracle model on CPU; returns tok/s."""
+    from mini_vllm_b200.models.loader import load_model
+    from mini_vllm_b200.engine.request import Request
+    from mini_vllm_b200.scheduler.scheduler import Scheduler
+    from oracle.model import OracleExecutor, OracleModel, reference_names
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    hf = qwen3_shape()
+    cfg = Config(hf_config=hf, kv_cache_num_blocks=16, max_num_batched_seqs=4, use_cuda_graph=False, seed=seed)
+    model = load_model(cfg, device="cpu")
+    weights = reference_names(dict(model.state_dict()), "qwen3", hf)
+    del model
+    omodel = OracleModel(weights, hf, "qwen3", 16, 256, device="cpu")
+    ex = OracleExecutor(omodel, 256)
+    reqs = config2_requests(seed)[:2]
+    n_req, n_dec = 2, 4
+    sch = Scheduler(cfg)
+    rs = [Request(r.prompt[:256], SamplingParams(max_tokens=n_dec, ignore_eos=True)) for r in reqs[:n_req]]
+    for r in rs:
+        sch.submit(r)
+    t0 = time.perf_counter()
+    tokens = 0
+    while not sch.finished and time.perf_counter() - t0 < 4 * budget_s:
+        batch = sch.schedule()
+        out = ex.execute(batch)
+        tokens += sum(len(r.tokens) - r.num_cached_tokens for r in batch.requests) if batch.type == 0 else len(out)
+        sch.update(batch, out)
+    dt = time.perf_counter() - t0
+    sample = f"{n_req} requests, prompts cut to <=256 tokens, {n_dec} generated tokens each, bf16 weights, per-token extrapolation"
+    return tokens / dt, threads, sample, dt
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for _ in range(max(1, min(args.steps, 3))):
+        v, threads, sample, dt = cpu_reference_sample()
+        vals.append(v)
+    value = statistics.median(vals)
+    line = {"impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD},
+            "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": round(value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    from mini_vllm_b200 import ops
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks, peak_kind = measured_peaks()
+
+    all_reqs = config2_requests(seed=0, n=64 * world)
+    mine = [all_reqs[i] for i in partition_by_tokens(all_reqs, world)[rank]]
+    engine = build_engine(local_rank)
+    dev = engine.executor.device
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        run_job(engine, mine)
+    sampler = ClockSampler(local_rank)
+    contexts = []
+    ex = engine.executor
+    sync_all()
+    if rank == 0:
+        sampler.start()
+    launches0, h2d0, d2h0 = ops.LaunchCounter.total, ex.h2d_bytes, ex.d2h_bytes
+    steps0 = engine.metrics.prefill_steps + engine.metrics.decode_steps
+    t0 = time.perf_counter()
+    tok = 0
+    cuda_ms = 0.0
+    for i in range(args.steps):
+        n, wall, ms = run_job(engine, mine, contexts if i == args.steps - 1 else None)
+        tok += n
+        cuda_ms += ms
+    sync_all()
+    wall_total = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    launches = ops.LaunchCounter.total - launches0
+    engine_steps = engine.metrics.prefill_steps + engine.metrics.decode_steps - steps0
+    h2d, d2h = ex.h2d_bytes - h2d0, ex.d2h_bytes - d2h0
+
+    stats = torch.tensor([cuda_ms, wall_total * 1e3, float(tok), float(launches)], dtype=torch.float64, device=dev)
+    if dist is not None:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        cuda_ms_max, wall_ms_max, tok_all, launches_all = mx[0].item(), mx[1].item(), sm[2].item(), sm[3].item()
+    else:
+        cuda_ms_max, wall_ms_max, tok_all, launches_all = cuda_ms, wall_total * 1e3, float(tok), float(launches)
+
+    if rank == 0:
+        roof = decode_roofline(engine, contexts, peaks)
+        roof["peak_kind"] = f"of {peak_kind}"
+        extras = kernel_extras(dev, peaks)
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            v, threads, sample, dt = cpu_reference_sample()
+            cpu = {"value": round(v, 2), "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample,
+                   "seconds": round(dt, 1)}
+        line = {
+            "metric": METRIC, "value": round(tok_all / (cuda_ms_max * 1e-3), 1), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(cuda_ms_max / args.steps, 2), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "requests_per_gpu": len(mine), "parallelism": f"replicas x{world}",
+                       "l2": "KV pool (28 layers, >126 MB per step) exceeds L2; kernel legs rotate distinct pools",
+                       "tokens_per_step_all_gpus": int(tok_all / args.steps)},
+            "e2e": {"value": round(tok_all / (wall_ms_max * 1e-3), 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": int(h2d / max(engine_steps, 1)),
+                    "d2h_bytes_per_step": int(d2h / max(engine_steps, 1)),
+                    "engine_steps_per_job": engine_steps // args.steps},
+            "gpu_launches": int(launches_all),
+            "clocks": clocks, "roofline": roof, "kernels": extras, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

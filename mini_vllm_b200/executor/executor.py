@@ -1,0 +1,207 @@
+"""Executor: model, KV pool, device-side batch packing, CUDA-graph decode, sampling.
+
+Counterpart of ``minivllm/executor/executor.py``.  The contract of ``_build_prefill_input`` /
+``_build_decode_input`` / ``_build_block_table`` (``:81-163``) is unchanged — same tensors, dtypes
+and shapes inside the same ``Context`` — but the per-token Python loops and the five pinned
+uploads per step are gone: the host gathers per-SEQUENCE facts (lengths, cached lengths, block
+lists, the new tokens) into one pinned int32 buffer with numpy, uploads it with a single copy, and
+a packing kernel expands it on the device.
+"""
+from __future__ import annotations
+
+import itertools
+import logging
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..engine.request import Request
+from ..models.layers.sampler import Sampler
+from ..models.loader import load_model
+from ..scheduler.batch import Batch
+from .context import Context
+from .graph import CudaGraphRunner
+
+log = logging.getLogger(__name__)
+
+
+class _Staging:
+    """A pinned host int32 buffer and its device twin, grown on demand; one upload per step."""
+
+    def __init__(self, device):
+        self.device = device
+        self.host = torch.empty(0, dtype=torch.int32)
+        self.dev = torch.empty(0, dtype=torch.int32, device=device)
+
+    def upload(self, parts: list[np.ndarray]) -> torch.Tensor:
+        n = sum(p.size for p in parts)
+        if self.host.numel() < n:
+            cap = max(n, 2 * self.host.numel(), 1 << 16)
+            self.host = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self.dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        view, cur = self.host.numpy(), 0
+        for p in parts:
+            view[cur:cur + p.size] = p
+            cur += p.size
+        self.dev[:n].copy_(self.host[:n], non_blocking=True)
+        return self.dev[:n]
+
+
+class Executor:
+    def __init__(self, config):
+        self.config = config
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.block_size = config.kv_cache_block_size
+        self.model = load_model(config, self.device)
+        self.sampler = Sampler(seed=config.seed)
+        self.status = ops.new_status(self.device)
+        self._stage = _Staging(self.device)
+        self.h2d_bytes = 0                   # bytes uploaded by the packing path (for the bench's e2e line)
+        self.d2h_bytes = 0
+        self.graph_runner = None
+        self._warmup_model()
+        self._init_kv_cache()
+        if config.use_cuda_graph:
+            log.info("capturing CUDA graphs for decode")
+            self.graph_runner = CudaGraphRunner(self.model, config, config.max_num_batched_seqs, self.status)
+            self.graph_runner.capture()
+
+    # ---- bring-up --------------------------------------------------------------------------------
+    def _warmup_model(self) -> None:
+        """A prefill of block-less zero-token requests before the KV pool exists (executor.py:62-78)."""
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+        self.execute(Batch(Batch.PREFILL, [Request([0] * 64) for _ in range(10)]))
+        torch.cuda.empty_cache()
+
+    def _init_kv_cache(self) -> None:
+        """Pool ``[2, layers, blocks, block_size, kv_heads, head_dim]``; layer l's K is ``[0, l]`` (executor.py:31-60)."""
+        cfg, hf = self.config, self.config.hf_config
+        free, total = torch.cuda.mem_get_info()
+        stats = torch.cuda.memory_stats()
+        peak, current = stats["allocated_bytes.all.peak"], stats["allocated_bytes.all.current"]
+        head_dim = getattr(hf, "head_dim", hf.hidden_size // hf.num_attention_heads)
+        block_bytes = 2 * hf.num_hidden_layers * self.block_size * hf.num_key_value_heads * head_dim * hf.dtype.itemsize
+        fit = int(total * cfg.gpu_memory_utilization - (total - free) - peak + current) // block_bytes
+        if fit <= 0:
+            raise RuntimeError("no memory left for the KV cache")
+        cfg.kv_cache_num_blocks = min(fit, cfg.kv_cache_num_blocks)
+        self.kv_cache = torch.empty(2, hf.num_hidden_layers, cfg.kv_cache_num_blocks, self.block_size,
+                                    hf.num_key_value_heads, head_dim, dtype=hf.dtype, device=self.device)
+        log.info("allocated %d KV blocks", cfg.kv_cache_num_blocks)
+        layer = 0
+        for module in self.model.modules():
+            if hasattr(module, "k_cache") and hasattr(module, "v_cache"):
+                module.k_cache, module.v_cache = self.kv_cache[0, layer], self.kv_cache[1, layer]
+                layer += 1
+
+    # ---- packing ---------------------------------------------------------------------------------
+    @staticmethod
+    def _per_seq(requests: list[Request]):
+        b = len(requests)
+        seq_len = np.fromiter((len(r.tokens) for r in requests), np.int32, b)
+        nblk = np.fromiter((len(r.blocks) for r in requests), np.int32, b)
+        blk_off = np.zeros(b + 1, np.int32)
+        np.cumsum(nblk, out=blk_off[1:])
+        blocks = np.fromiter(itertools.chain.from_iterable(r.blocks for r in requests), np.int32, int(blk_off[-1]))
+        return seq_len, nblk, blk_off, blocks
+
+    def _build_prefill_input(self, requests: list[Request]) -> tuple[torch.Tensor, Context]:
+        b = len(requests)
+        seq_len, nblk, blk_off, blocks = self._per_seq(requests)
+        cached = np.fromiter((r.num_cached_tokens for r in requests), np.int32, b)
+        q_len = seq_len - cached
+        t = int(q_len.sum())
+        new_tokens = np.fromiter(
+            itertools.chain.from_iterable(r.tokens[r.num_cached_tokens:] if r.num_cached_tokens else r.tokens
+                                          for r in requests), np.int32, t)
+        meta = self._stage.upload([seq_len, cached, blk_off, blocks, new_tokens])
+        self.h2d_bytes += meta.numel() * 4
+        width = max(int(nblk.max()), 1)
+        out = ops.pack_prefill(meta, b, t, int(blk_off[-1]), width, self.block_size, bool(cached.any()), self.status)
+        ctx = Context(prefill=True, positions=out["positions"], cu_seqlens_q=out["cu_seqlens_q"],
+                      cu_seqlens_k=out["cu_seqlens_k"], slot_mapping=out["slot_mapping"],
+                      max_seqlen_q=int(q_len.max()), max_seqlen_k=int(seq_len.max()),
+                      block_table=out["block_table"], status=self.status)
+        return out["input_ids"], ctx
+
+    def _decode_meta(self, requests: list[Request]):
+        b = len(requests)
+        seq_len, nblk, blk_off, blocks = self._per_seq(requests)
+        last = np.fromiter((r.tokens[-1] for r in requests), np.int32, b)
+        meta = self._stage.upload([seq_len, blk_off, blocks, last, np.full(b, -1, np.int32)])
+        self.h2d_bytes += meta.numel() * 4
+        return meta, int(blk_off[-1]), int(nblk.max())
+
+    def _build_decode_input(self, requests: list[Request]) -> tuple[torch.Tensor, Context]:
+        b = len(requests)
+        meta, nblocks, width = self._decode_meta(requests)
+        gr = self.graph_runner
+        if gr is not None and gr.max_batch_size >= b:
+            padded = gr.padded_size(b)
+            ops.pack_decode(meta, b, nblocks, width, self.block_size, gr.input_ids, gr.positions, gr.slot_mapping,
+                            gr.cache_seqlens, gr.block_table, padded_seqs=padded, status=self.status)
+            return gr.input_ids[:b], gr.static_context(b)
+        dev = self.device
+        ids, pos = torch.empty(b, dtype=torch.int64, device=dev), torch.empty(b, dtype=torch.int64, device=dev)
+        slot, lens = torch.empty(b, dtype=torch.int32, device=dev), torch.empty(b, dtype=torch.int32, device=dev)
+        table = torch.empty(b, width, dtype=torch.int32, device=dev)
+        ops.pack_decode(meta, b, nblocks, width, self.block_size, ids, pos, slot, lens, table, status=self.status)
+        return ids, Context(prefill=False, positions=pos, slot_mapping=slot, cache_seqlens=lens, block_table=table,
+                            status=self.status)
+
+    def _build_block_table(self, requests: list[Request]) -> torch.Tensor:
+        """Block table alone, right-padded with -1 (executor.py:156-163); packed on the device."""
+        b = len(requests)
+        _, nblk, blk_off, blocks = self._per_seq(requests)
+        zeros = np.zeros(b, np.int32)
+        meta = self._stage.upload([zeros, zeros, blk_off, blocks])
+        width = max(int(nblk.max()), 1)
+        return ops.pack_prefill(meta, b, 0, int(blk_off[-1]), width, self.block_size, True, self.status)["block_table"]
+
+    # ---- sampling -------------------------------------------------------------------------------
+    def _build_sample_input(self, requests: list[Request]):
+        """Tensors only when some request needs them (executor.py:165-191)."""
+        temps = [r.sampling_params.temperature for r in requests]
+        ks = [r.sampling_params.top_k for r in requests]
+        ps = [r.sampling_params.top_p for r in requests]
+        t = k = p = None
+        if any(x > 0 for x in ks) or any(x < 1.0 for x in ps):
+            k = torch.tensor(ks, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+            p = torch.tensor(ps, dtype=torch.float32).pin_memory().to(self.device, non_blocking=True)
+        if any(x != 1.0 for x in temps):
+            t = torch.tensor(temps, dtype=torch.float32).pin_memory().to(self.device, non_blocking=True)
+        return t, k, p
+
+    def sample(self, logits: torch.Tensor, batch: Batch) -> list[int]:
+        temperatures, top_k, top_p = self._build_sample_input(batch.requests)
+        tokens = self.sampler(logits, temperatures, top_p=top_p, top_k=top_k)
+        self.d2h_bytes += tokens.numel() * 8
+        return tokens.tolist()
+
+    # ---- forward ---------------------------------------------------------------------------------
+    def prefill(self, ctx: Context, input_ids: torch.Tensor) -> torch.Tensor:
+        return self.model(ctx, input_ids, ctx.positions)
+
+    def decode(self, ctx: Context, input_ids: torch.Tensor) -> torch.Tensor:
+        gr = self.graph_runner
+        if gr is not None and gr.max_batch_size >= input_ids.size(0):
+            return gr.replay(ctx, input_ids)
+        return self.model(ctx, input_ids, ctx.positions)
+
+    def forward(self, ctx: Context, tokens: torch.Tensor) -> torch.Tensor:
+        return self.prefill(ctx, tokens) if ctx.prefill else self.decode(ctx, tokens)
+
+    @torch.inference_mode()
+    def execute(self, batch: Batch) -> list[int]:
+        if batch.type == Batch.PREFILL:
+            input_ids, ctx = self._build_prefill_input(batch.requests)
+        else:
+            input_ids, ctx = self._build_decode_input(batch.requests)
+        logits = self.forward(ctx, input_ids)
+        return self.sample(logits, batch)
+
+    def check_device_status(self) -> None:
+        """Synchronising check of the kernels' error word (bad slots / block ids / positions)."""
+        ops.check_status(self.status)

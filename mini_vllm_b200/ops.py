@@ -14,6 +14,15 @@ _DEV_ERRORS = {1: "slot outside the KV pool", 2: "block id outside the KV pool",
                5: "sequence length does not fit its block list"}
 
 
+class LaunchCounter:
+    """Counts kernels of this library enqueued through the wrappers below (graph replays add theirs)."""
+    total = 0
+
+    @classmethod
+    def add(cls, n: int) -> None:
+        cls.total += n
+
+
 def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
@@ -71,6 +80,7 @@ def pack_prefill(meta: torch.Tensor, num_seqs: int, num_tokens: int, num_blocks_
         B, T, table_width, block_size, _ptr(out["input_ids"]), _ptr(out["positions"]), _ptr(out["slot_mapping"]),
         _ptr(out["cu_seqlens_q"]), _ptr(out["cu_seqlens_k"]), _ptr(out["block_table"]), _ptr(status), _stream())
     _cabi.check(rc, "mvb_pack_prefill")
+    LaunchCounter.add(1)
     return out
 
 
@@ -105,6 +115,7 @@ def pack_decode(meta: torch.Tensor, num_seqs: int, num_blocks_total: int, table_
         block_size, _ptr(input_ids), _ptr(positions), _ptr(slot_mapping), _ptr(cache_seqlens), _ptr(block_table),
         _ptr(status), _stream())
     _cabi.check(rc, "mvb_pack_decode")
+    LaunchCounter.add(1)
 
 
 def rope_kv_write(q: torch.Tensor | None, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor | None,
@@ -137,6 +148,7 @@ def rope_kv_write(q: torch.Tensor | None, k: torch.Tensor, v: torch.Tensor, posi
         _ptr(k_cache) if slot_mapping is not None else None, _ptr(v_cache) if slot_mapping is not None else None,
         num_slots, T, hq, hkv, d, 1 if k_in_place else 0, _ptr(status), _stream())
     _cabi.check(rc, "mvb_rope_kv_write")
+    LaunchCounter.add(1)
 
 
 def decode_workspace(max_seqs: int, num_q_heads: int, head_dim: int, device) -> torch.Tensor:
@@ -152,6 +164,7 @@ def decode_plan(cache_seqlens: torch.Tensor, window_left: int, num_q_heads: int,
     rc = _cabi.load().mvb_decode_plan(_ptr(cache_seqlens), cache_seqlens.numel(), window_left, num_q_heads,
                                       num_kv_heads, head_dim, _ptr(workspace), workspace.numel(), _stream())
     _cabi.check(rc, "mvb_decode_plan")
+    LaunchCounter.add(1)
 
 
 def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_seqlens: torch.Tensor,
@@ -172,6 +185,7 @@ def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, c
         block_table.stride(0), block_table.shape[1], B, hq, hkv, d, float(scale), window_left, _ptr(out),
         out.stride(0), _ptr(workspace), workspace.numel(), _ptr(status), _stream())
     _cabi.check(rc, "mvb_decode_attn")
+    LaunchCounter.add(2)
     return out
 
 
@@ -199,6 +213,7 @@ def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q
         _ptr(block_table), tstride, bs, cu_seqlens_q.numel() - 1, Tq, int(max_seqlen_q), hq, hkv, d, float(scale),
         window_left, _ptr(out), out.stride(0), _ptr(status), _stream())
     _cabi.check(rc, "mvb_prefill_attn")
+    LaunchCounter.add(1)
     return out
 
 
@@ -217,4 +232,5 @@ def sample(logits: torch.Tensor, temperatures: torch.Tensor | None = None, top_k
     rc = _cabi.load().mvb_sample(_ptr(logits), logits.stride(0), B, V, _ptr(temperatures), _ptr(top_k),
                                  seed & (2**64 - 1), offset & (2**64 - 1), _ptr(out), None, _stream())
     _cabi.check(rc, "mvb_sample")
+    LaunchCounter.add(1)
     return out

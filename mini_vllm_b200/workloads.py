@@ -82,6 +82,16 @@ def assign_blocks(g: torch.Generator, lengths: list[int], pool_blocks: int,
     return tables
 
 
+def table_tensor(tables: list[list[int]], width: int | None = None, pad: int = -1) -> torch.Tensor:
+    """Block lists -> int32 ``[B, W]`` right-padded with ``pad`` (the Context block-table layout)."""
+    width = width or max(1, max(len(t) for t in tables))
+    out = torch.full((len(tables), width), pad, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        if t:
+            out[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    return out
+
+
 @dataclass
 class SingleLayerCase:
     """One attention layer's worth of ragged work (configs 1, 3, 4)."""

@@ -32,8 +32,8 @@ def _sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
     kf = k.float().transpose(0, 1).repeat_interleave(g, dim=0)      # [Hq,Tk,D]
     vf = v.float().transpose(0, 1).repeat_interleave(g, dim=0)
     s = torch.matmul(qf, kf.transpose(1, 2)) * scale                # [Hq,Tq,Tk]
-    p = torch.arange(q_pos0, q_pos0 + tq).unsqueeze(1)
-    j = torch.arange(tk).unsqueeze(0)
+    p = torch.arange(q_pos0, q_pos0 + tq, device=q.device).unsqueeze(1)
+    j = torch.arange(tk, device=q.device).unsqueeze(0)
     visible = j <= p
     if window_left >= 0:
         visible &= j >= p - window_left
@@ -62,7 +62,7 @@ def prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     """
     d = q.shape[-1]
     scale = d ** -0.5 if scale is None else scale
-    out = torch.zeros(q.shape, dtype=torch.float32)
+    out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
     cq, ck = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
     for s in range(len(cq) - 1):
         ql, kl = cq[s + 1] - cq[s], ck[s + 1] - ck[s]
@@ -82,7 +82,7 @@ def decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     """q ``[B,Hq,D]`` (one token per sequence) against ``cache_seqlens[b]`` cached keys."""
     d = q.shape[-1]
     scale = d ** -0.5 if scale is None else scale
-    out = torch.zeros(q.shape, dtype=torch.float32)
+    out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
     for b, n in enumerate(cache_seqlens.tolist()):
         if n == 0:
             continue

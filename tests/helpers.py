@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from mini_vllm_b200.workloads import BLOCK_SIZE, cdiv, generator, randn_bf16
+from mini_vllm_b200.workloads import BLOCK_SIZE, cdiv, generator, randn_bf16, table_tensor  # noqa: F401
 
 ATTN_MAX_ABS = 2e-2     # tolerance of the attention outputs against the fp32 oracle (bf16 inputs)
 ATTN_MEAN_ABS = 2e-3
@@ -27,14 +27,6 @@ def fill_paged(g: torch.Generator, lens: list[int], tables: list[list[int]], num
             k_pool[blk, :hi - lo] = k[lo:hi]
             v_pool[blk, :hi - lo] = v[lo:hi]
     return k_pool, v_pool
-
-
-def table_tensor(tables: list[list[int]], width: int | None = None, pad: int = -1) -> torch.Tensor:
-    width = width or max(len(t) for t in tables)
-    out = torch.full((len(tables), width), pad, dtype=torch.int32)
-    for i, t in enumerate(tables):
-        out[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
-    return out
 
 
 def sequential_tables(g: torch.Generator, lens: list[int], num_blocks: int, block_size: int = BLOCK_SIZE):
