@@ -156,15 +156,25 @@ def decode_roofline(engine, contexts, peaks):
         ws = ops.decode_workspace(b, hq, d, dev)
         out = torch.empty_like(q)
         ops.decode_plan(seqlens, -1, hq, hkv, d, ws)
-        for layer in range(3):                                   # warm-up launches
-            ops.decode_attn(q, ex.kv_cache[0, layer], ex.kv_cache[1, layer], seqlens, bt, d ** -0.5, -1, ws, out=out)
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(layers + 1)]
-        evs[0].record()
-        for layer in range(layers):                              # distinct layer pools: no L2 reuse between launches
-            ops.decode_attn(q, ex.kv_cache[0, layer], ex.kv_cache[1, layer], seqlens, bt, d ** -0.5, -1, ws, out=out)
-            evs[layer + 1].record()
+        def all_layers():                                        # distinct layer pools: no L2 reuse between launches
+            for layer in range(layers):
+                ops.decode_attn(q, ex.kv_cache[0, layer], ex.kv_cache[1, layer], seqlens, bt, d ** -0.5, -1, ws, out=out)
+        all_layers()                                             # warm-up, also outside any capture
         torch.cuda.synchronize()
-        total_ms += sum(evs[i].elapsed_time(evs[i + 1]) for i in range(layers))
+        # launch the 28 layers back to back from a CUDA graph, as the engine does, so that the
+        # event-to-event time is device time and not the host's launch rate
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            all_layers()
+        graph.replay()
+        reps = 3
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        total_ms += e0.elapsed_time(e1) / reps
         total_bytes += layers * decode_kv_bytes(QWEN3_0P6B, lens)
         launches += layers
     achieved = total_bytes / (total_ms * 1e-3) / 1e9 if total_ms else 0.0
@@ -172,7 +182,7 @@ def decode_roofline(engine, contexts, peaks):
             "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None, "kernel": "decode_attn_kernel<128,8>",
             "launches_timed": launches, "avg_launch_us": round(total_ms * 1e3 / max(launches, 1), 2),
             "avg_bytes_per_launch": int(total_bytes / max(launches, 1)),
-            "note": "algorithmic K+V bytes of recorded decode steps (incl. combine kernel time); peak = STREAM copy"}
+            "note": "algorithmic K+V bytes of recorded decode steps, 28 layer launches replayed from a CUDA graph; peak = STREAM copy"}
 
 
 def kernel_extras(dev, peaks):

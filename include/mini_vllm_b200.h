@@ -133,17 +133,17 @@ int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, co
  * Causal varlen prefill attention on the tcgen05 tensor cores.
  * Replaces flash_attn_varlen_func as called at minivllm/models/layers/attention.py:84-87.
  *   q [total_q, num_q_heads, head_dim]; sequence s owns rows cu_seqlens_q[s]..cu_seqlens_q[s+1].
- *   block_table == NULL: k, v are dense [total_k, num_kv_heads, head_dim] (row stride
- *     kv_row_stride) sliced by cu_seqlens_k.
+ *   block_table == NULL: k, v are dense [total_k, num_kv_heads, head_dim] (row strides
+ *     k_row_stride / v_row_stride; kv_rows = total_k) sliced by cu_seqlens_k.
  *   block_table != NULL: k, v are the paged pool (kv_rows = num_blocks*block_size slots,
- *     kv_row_stride = num_kv_heads*head_dim) and keys 0..k_len-1 of sequence s are gathered
+ *     both row strides = num_kv_heads*head_dim) and keys 0..k_len-1 of sequence s are gathered
  *     through row s of the table (the prefix-cache case, attention.py:79-83).
  *   Query i of a sequence sits at position p = k_len - q_len + i and sees keys
  *   max(0, p - window_left) <= j <= p.
  * Supported: head_dim 128 (256 planned), any GQA ratio, block_size a multiple of 128.
  */
-int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void* k, const void* v, int64_t kv_row_stride,
-                     int64_t kv_rows, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void* k, int64_t k_row_stride, const void* v,
+                     int64_t v_row_stride, int64_t kv_rows, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
                      const int32_t* block_table, int64_t table_stride, int block_size, int num_seqs,
                      int total_q, int max_seqlen_q, int num_q_heads, int num_kv_heads, int head_dim,
                      float scale, int window_left, void* out, int64_t out_row_stride, int32_t* dev_status,

@@ -19,8 +19,9 @@
 //
 // A segment (the part of a sequence inside one CTA's range) that covers the whole sequence is
 // normalised and written straight to the output; otherwise the CTA writes a partial
-// (normalised O in fp32 + log2-sum-exp) and the combine kernel, a separate launch, merges the
-// partials.  No kernel ever waits on another CTA.
+// (normalised O in fp32 + log2-sum-exp), bumps the sequence's arrival counter, and the CTA that
+// arrives last merges the partials (the combine pass) and re-arms the counter.  Nothing ever
+// waits on another CTA, so the launch cannot hang and needs no co-residency.
 #include "common.cuh"
 #include "host_util.cuh"
 #include "mini_vllm_b200.h"
@@ -28,27 +29,56 @@
 
 namespace mvb {
 
+// Optional timeline probe (compiled in only with -DMVB_DECODE_TRACE): thread 0 of every CTA stamps
+// the SM clock at a few points so that fixed costs can be attributed.
+#ifdef MVB_DECODE_TRACE
+__device__ unsigned long long* g_decode_trace = nullptr;
+#define MVB_TRACE(i)                                                                          \
+  do {                                                                                        \
+    if (threadIdx.x == 0 && blockIdx.y == 0 && g_decode_trace != nullptr) {                   \
+      unsigned long long t_;                                                                  \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                   \
+      g_decode_trace[blockIdx.x * 16 + (i)] = t_;                                             \
+    }                                                                                         \
+  } while (0)
+#else
+#define MVB_TRACE(i)
+#endif
+
 constexpr int kMaxCtas = 160;          // workspace is sized for this many persistent CTAs
 constexpr int kPlanThreads = 256;
 constexpr int kMinTilesPerCta = 2;
+constexpr int kMaxPartsPerSeq = 32;   // target bound on the partials one sequence is split into
 
 struct DecodeHeader {                  // first 32 bytes of the workspace (device memory)
   int32_t total_tiles, per_cta, num_ctas, cta_tokens, num_seqs, window_left, pad0, pad1;
 };
 
+// What a CTA needs to start streaming, written by the plan kernel so that the attention kernel
+// begins with ONE 32-byte load instead of a chain of dependent ones.
+struct alignas(32) CtaDesc {
+  int32_t t0, t1;             // this CTA's tile range [t0, t1) (t0 >= t1: no work)
+  int32_t b;                  // sequence holding tile t0
+  int32_t tp0, tp1;           // that sequence's tile range
+  int32_t n;                  // its context length
+  int32_t per;                // tiles per CTA
+  int32_t pad;
+};
+
 struct DecodeLayout {                  // byte offsets inside the workspace
-  size_t first_seq, lse, o, tile_prefix, total;
+  size_t descs, lse, o, tile_prefix, total;       // arrival counters follow tile_prefix[num_seqs + 1]
 };
 
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 static DecodeLayout decode_layout(int max_seqs, int hq, int d) {
   DecodeLayout l;
-  l.first_seq = sizeof(DecodeHeader);
-  l.lse = align_up(l.first_seq + sizeof(int32_t) * (kMaxCtas + 1), 256);
+  l.descs = sizeof(DecodeHeader);
+  l.lse = align_up(l.descs + sizeof(CtaDesc) * kMaxCtas, 256);
   l.o = align_up(l.lse + sizeof(float) * kMaxCtas * 2 * hq, 256);
   l.tile_prefix = align_up(l.o + sizeof(float) * kMaxCtas * 2 * static_cast<size_t>(hq) * d, 256);
-  l.total = align_up(l.tile_prefix + sizeof(int32_t) * (static_cast<size_t>(max_seqs) + 1), 256);
+  l.total = align_up(l.tile_prefix + sizeof(int32_t) * (static_cast<size_t>(max_seqs) + 1) +
+                         sizeof(int32_t) * static_cast<size_t>(max_seqs) * hq, 256);
   return l;
 }
 
@@ -78,35 +108,49 @@ __device__ __forceinline__ int visible_start(int n, int window_left) {
 
 __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int32_t* __restrict__ cache_seqlens,
                                                                    int num_seqs, int window_left, int cta_tokens,
-                                                                   int num_ctas, DecodeHeader* hdr,
-                                                                   int32_t* first_seq, int32_t* tile_prefix) {
+                                                                   int num_ctas, int num_counters,
+                                                                   DecodeHeader* hdr, CtaDesc* descs,
+                                                                   int32_t* tile_prefix) {
+  __shared__ int max_tiles_s;
+  if (threadIdx.x == 0) max_tiles_s = 0;
+  for (int i = threadIdx.x; i < num_counters; i += kPlanThreads) tile_prefix[num_seqs + 1 + i] = 0;
+  __syncthreads();
   block_exclusive_scan<kPlanThreads>(
       [&](int b) {
         const int n = cache_seqlens[b];
         if (n <= 0) return 0;
         const int start_al = visible_start(n, window_left) / cta_tokens * cta_tokens;
-        return (n - start_al + cta_tokens - 1) / cta_tokens;
+        const int tiles = (n - start_al + cta_tokens - 1) / cta_tokens;
+        atomicMax(&max_tiles_s, tiles);
+        return tiles;
       },
       num_seqs, tile_prefix);
   const int total = tile_prefix[num_seqs];
   int per = (total + num_ctas - 1) / num_ctas;
   per = per < kMinTilesPerCta ? kMinTilesPerCta : per;
+  // one CTA merges all partials of a sequence: keep that bounded (a few-sequence batch would
+  // otherwise be cut into a hundred slivers whose merge costs more than the streaming)
+  const int per_for_merge = (max_tiles_s + kMaxPartsPerSeq - 1) / kMaxPartsPerSeq;
+  per = per < per_for_merge ? per_for_merge : per;
   if (threadIdx.x == 0) {
     hdr->total_tiles = total; hdr->per_cta = per; hdr->num_ctas = num_ctas; hdr->cta_tokens = cta_tokens;
     hdr->num_seqs = num_seqs; hdr->window_left = window_left; hdr->pad0 = 0; hdr->pad1 = 0;
   }
-  for (int c = threadIdx.x; c <= num_ctas; c += kPlanThreads) {
+  for (int c = threadIdx.x; c < num_ctas; c += kPlanThreads) {
     const int64_t t = static_cast<int64_t>(c) * per;
-    int b = num_seqs;
+    CtaDesc d;
+    d.t0 = t < total ? static_cast<int32_t>(t) : total;
+    d.t1 = t + per < total ? static_cast<int32_t>(t + per) : total;
+    d.b = num_seqs; d.tp0 = d.tp1 = d.n = 0; d.per = per; d.pad = 0;
     if (t < total) {                   // last b with tile_prefix[b] <= t
       int lo = 0, hi = num_seqs;
       while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
         if (tile_prefix[mid] <= t) lo = mid; else hi = mid;
       }
-      b = lo;
+      d.b = lo; d.tp0 = tile_prefix[lo]; d.tp1 = tile_prefix[lo + 1]; d.n = cache_seqlens[lo];
     }
-    first_seq[c] = b;
+    descs[c] = d;
   }
 }
 
@@ -125,10 +169,11 @@ struct DecodeParams {
   float scale_log2;
   int window_left;
   const DecodeHeader* hdr;
-  const int32_t* first_seq;
+  const CtaDesc* descs;
   const int32_t* tile_prefix;
   float* part_lse;
   float* part_o;
+  int32_t* arrivals;            // [num_seqs * gridDim.y], zero between launches
   int* dev_status;
 };
 
@@ -160,10 +205,30 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   const int kvh = blockIdx.y * HPC + head_local;
   const int G = p.group;
   const int c = blockIdx.x;
-  const int total = p.hdr->total_tiles, per = p.hdr->per_cta;
-  const int t0 = c * per;
-  if (t0 >= total) return;                                   // CTA-uniform
-  const int t1 = min(total, t0 + per);
+  MVB_TRACE(0);
+  CtaDesc desc;
+  {
+    const int4* dp = reinterpret_cast<const int4*>(p.descs + c);
+    const int4 lo = __ldg(dp), hi = __ldg(dp + 1);
+    desc.t0 = lo.x; desc.t1 = lo.y; desc.b = lo.z; desc.tp0 = lo.w;
+    desc.tp1 = hi.x; desc.n = hi.y; desc.per = hi.z; desc.pad = hi.w;
+  }
+  const int per = desc.per, t0 = desc.t0, t1 = desc.t1;
+  // rows with an empty context (graph padding) produce zeros; spread over the CTAs, and done by
+  // idle CTAs first so it stays off the path of the ones that stream
+  auto zero_empty_rows = [&]() {
+    for (int b = c; b < p.num_seqs; b += gridDim.x) {
+      if (p.cache_seqlens[b] <= 0) {
+        __nv_bfloat16* row = p.out + b * p.out_stride + static_cast<int64_t>(blockIdx.y) * HPC * G * D;
+        for (int e = threadIdx.x; e < HPC * G * D; e += NW * 32) row[e] = __float2bfloat16_rn(0.f);
+      }
+    }
+  };
+  MVB_TRACE(1);
+  if (t0 >= t1) {                                            // CTA-uniform: nothing to stream
+    zero_empty_rows();
+    return;
+  }
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -181,8 +246,13 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   __syncthreads();
 
   // ---- producer side: the same tile walk as the consumer, NST-1 tiles ahead --------------------
+  auto seq_from_desc = [&](SeqView& v) {
+    v.b = desc.b; v.tp0 = desc.tp0; v.tp1 = desc.tp1; v.n = desc.n;
+    v.start = visible_start(v.n, p.window_left);
+    v.start_al = v.start / CT * CT;
+  };
   SeqView fs;
-  load_seq<CT>(fs, p.first_seq[c], p);
+  seq_from_desc(fs);
   int ft = t0, nfetch = 0, blk_base = -1, blk_reg = -1;
   auto fetch_next = [&]() -> bool {
     while (true) {
@@ -221,12 +291,14 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       return true;
     }
   };
+  MVB_TRACE(2);
 #pragma unroll
   for (int i = 0; i < NST - 1; ++i) fetch_next();
+  MVB_TRACE(3);
 
   // ---- consumer side ------------------------------------------------------------------------------
   SeqView cs;
-  load_seq<CT>(cs, p.first_seq[c], p);
+  seq_from_desc(cs);
   const int first_b = cs.b;
   int t = t0, ncomp = 0;
   bool dead = false;
@@ -266,6 +338,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
         dead = true;
         continue;
       }
+      if (ncomp == 0) MVB_TRACE(4);
       ++ncomp;
       const uint32_t kbase = my_stages + st * C::STAGE_BYTES;
       const uint32_t vbase = kbase + C::TILE_BYTES;
@@ -335,6 +408,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       __syncwarp();
     }
 
+    MVB_TRACE(5);
     // ---- end of segment: merge the warps that share a head, then write output or partial --------
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
@@ -357,70 +431,136 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       }
     }
     __syncthreads();
+    const float* __restrict__ plse = p.part_lse;
+    const float* __restrict__ po = p.part_o;
+    float* __restrict__ plse_w = p.part_lse;
+    float* __restrict__ po_w = p.part_o;
+    __nv_bfloat16* __restrict__ outp = p.out;
+    const int heads = HPC * G;                               // query heads of this CTA
+    const int items = heads * D / 4;                         // 4-dim groups to produce
     {
       const int slot = (b == first_b) ? 0 : 1;
-      for (int e = threadIdx.x; e < HPC * G * D; e += NW * 32) {
-        const int hl = e / (G * D), g = (e / D) % G, dim = e % D;
+      for (int it = threadIdx.x; it < items; it += NW * 32) {
+        const int h = (it * 4) / D, dim = (it * 4) % D;      // h = hl * G + g
+        const int hl = h / G, g = h - hl * G;
         float M = -INFINITY;
 #pragma unroll
         for (int sb = 0; sb < C::TS; ++sb) M = fmaxf(M, fin[((sb * HPC + hl) * G + g) * C::FIN_STRIDE + D]);
-        float L = 0.f, acc = 0.f;
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int sb = 0; sb < C::TS; ++sb) {
           const float* f = fin + ((sb * HPC + hl) * G + g) * C::FIN_STRIDE;
           const float w = f[D] == -INFINITY ? 0.f : fast_exp2(f[D] - M);
+          const float4 v = *reinterpret_cast<const float4*>(f + dim);
           L += f[D + 1] * w;
-          acc += f[dim] * w;
+          acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
         }
-        const float val = L > 0.f ? acc / L : 0.f;
-        const int qh = (blockIdx.y * HPC + hl) * G + g;
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+        const int qh = blockIdx.y * heads + h;
         if (whole) {
-          p.out[b * p.out_stride + static_cast<int64_t>(qh) * D + dim] = __float2bfloat16_rn(val);
+          uint2 w2;
+          w2.x = pack_bf16(acc.x, acc.y); w2.y = pack_bf16(acc.z, acc.w);
+          *reinterpret_cast<uint2*>(outp + b * p.out_stride + static_cast<int64_t>(qh) * D + dim) = w2;
         } else {
           const int64_t pi = (static_cast<int64_t>(c) * 2 + slot) * p.hq + qh;
-          p.part_o[pi * D + dim] = val;
-          if (dim == 0) p.part_lse[pi] = L > 0.f ? M + log2f(L) : -INFINITY;
+          *reinterpret_cast<float4*>(po_w + pi * D + dim) = acc;
+          if (dim == 0) plse_w[pi] = L > 0.f ? M + log2f(L) : -INFINITY;
+        }
+      }
+    }
+    MVB_TRACE(6);
+    if (!whole) {
+      // combine pass without waiting: publish the partial, count the arrival; whoever arrives last
+      // finds every partial of this sequence in memory and merges them
+      __shared__ int is_last;
+      const int c1 = cs.tp0 / per, c2 = (cs.tp1 - 1) / per;
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int32_t* cnt = p.arrivals + static_cast<int64_t>(b) * gridDim.y + blockIdx.y;
+        const int prev = atomicAdd(cnt, 1);
+        is_last = (prev == c2 - c1);
+        if (is_last) *cnt = 0;                               // re-arm for the next launch
+      }
+      __syncthreads();
+      MVB_TRACE(7);
+      if (is_last) {
+        __threadfence();
+        constexpr int HEADS = HPC * 8;                       // upper bound of HPC * G
+        constexpr int PC = 32;                               // partials weighted per pass
+        constexpr int MAX_ITEMS = (HEADS * D / 4 + NW * 32 - 1) / (NW * 32);
+        int* m_enc = reinterpret_cast<int*>(fin);            // per-head max of the partial LSEs, order-encoded
+        float* w_s = fin + HEADS;                            // [PC][heads] weights of the current pass
+        const int nparts = c2 - c1 + 1;
+        const bool first_is_head = (cs.tp0 % per) == 0;      // does CTA c1's range start at this sequence?
+        auto part_index = [&](int cc, int qh) -> int64_t {
+          const int sl = (cc > c1 || first_is_head) ? 0 : 1;
+          return (static_cast<int64_t>(cc) * 2 + sl) * p.hq + qh;
+        };
+        if (threadIdx.x < HEADS) m_enc[threadIdx.x] = INT_MIN;
+        __syncthreads();
+        for (int i = threadIdx.x; i < nparts * heads; i += NW * 32) {
+          const int h = i % heads;
+          const int bits = __float_as_int(__ldcg(plse + part_index(c1 + i / heads, blockIdx.y * heads + h)));
+          atomicMax(&m_enc[h], bits >= 0 ? bits : bits ^ 0x7fffffff);
+        }
+        __syncthreads();
+        float4 acc[MAX_ITEMS];
+        float wsum[MAX_ITEMS];
+#pragma unroll
+        for (int k = 0; k < MAX_ITEMS; ++k) { acc[k] = make_float4(0.f, 0.f, 0.f, 0.f); wsum[k] = 0.f; }
+        for (int p0 = 0; p0 < nparts; p0 += PC) {
+          const int pn = min(PC, nparts - p0);
+          for (int i = threadIdx.x; i < pn * heads; i += NW * 32) {
+            const int h = i % heads;
+            const int enc = m_enc[h];
+            const float M = __int_as_float(enc >= 0 ? enc : enc ^ 0x7fffffff);
+            const float lse = __ldcg(plse + part_index(c1 + p0 + i / heads, blockIdx.y * heads + h));
+            w_s[i] = lse == -INFINITY ? 0.f : fast_exp2(lse - M);
+          }
+          __syncthreads();
+#pragma unroll
+          for (int k = 0; k < MAX_ITEMS; ++k) {
+            const int it = threadIdx.x + k * NW * 32;
+            if (it < items) {
+              const int h = (it * 4) / D, dim = (it * 4) % D, qh = blockIdx.y * heads + h;
+#pragma unroll 8
+              for (int j = 0; j < pn; ++j) {                 // independent 16-byte loads: they pipeline
+                const float w = w_s[j * heads + h];
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(po + part_index(c1 + p0 + j, qh) * D + dim));
+                acc[k].x = fmaf(w, v.x, acc[k].x); acc[k].y = fmaf(w, v.y, acc[k].y);
+                acc[k].z = fmaf(w, v.z, acc[k].z); acc[k].w = fmaf(w, v.w, acc[k].w);
+                wsum[k] += w;
+              }
+            }
+          }
+          __syncthreads();
+        }
+#pragma unroll
+        for (int k = 0; k < MAX_ITEMS; ++k) {
+          const int it = threadIdx.x + k * NW * 32;
+          if (it < items) {
+            const int h = (it * 4) / D, dim = (it * 4) % D, qh = blockIdx.y * heads + h;
+            const float inv = wsum[k] > 0.f ? 1.f / wsum[k] : 0.f;
+            uint2 w2;
+            w2.x = pack_bf16(acc[k].x * inv, acc[k].y * inv); w2.y = pack_bf16(acc[k].z * inv, acc[k].w * inv);
+            *reinterpret_cast<uint2*>(outp + b * p.out_stride + static_cast<int64_t>(qh) * D + dim) = w2;
+          }
         }
       }
     }
     __syncthreads();
   }
 
+  MVB_TRACE(8);
+  zero_empty_rows();
+  MVB_TRACE(9);
+
   // a wait that gave up may leave copies in flight: give them a bounded chance to land
   if (dead) {
     for (int i = ncomp; i < nfetch; ++i) mbar_wait(&bars[i % NST], (i / NST) & 1, 1u << 16);
-  }
-}
-
-// ---- combine ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams p, int d) {
-  const int b = blockIdx.x;
-  const int tp0 = p.tile_prefix[b], tp1 = p.tile_prefix[b + 1];
-  const int per = p.hdr->per_cta;
-  const int n_el = p.hq * d;
-  if (tp1 == tp0) {                                          // empty context (graph padding): zeros
-    for (int e = threadIdx.x; e < n_el; e += blockDim.x) p.out[b * p.out_stride + e] = __float2bfloat16_rn(0.f);
-    return;
-  }
-  const int c1 = tp0 / per, c2 = (tp1 - 1) / per;
-  if (c1 == c2) return;                                      // one CTA held the whole sequence
-  for (int e = threadIdx.x; e < n_el; e += blockDim.x) {
-    const int qh = e / d, dim = e - qh * d;
-    float M = -INFINITY;
-    for (int c = c1; c <= c2; ++c) {
-      const int slot = p.first_seq[c] == b ? 0 : 1;
-      M = fmaxf(M, p.part_lse[(static_cast<int64_t>(c) * 2 + slot) * p.hq + qh]);
-    }
-    float W = 0.f, acc = 0.f;
-    for (int c = c1; c <= c2; ++c) {
-      const int slot = p.first_seq[c] == b ? 0 : 1;
-      const int64_t pi = (static_cast<int64_t>(c) * 2 + slot) * p.hq + qh;
-      const float lse = p.part_lse[pi];
-      const float w = lse == -INFINITY ? 0.f : fast_exp2(lse - M);
-      W += w;
-      acc += w * p.part_o[pi * d + dim];
-    }
-    p.out[b * p.out_stride + e] = __float2bfloat16_rn(W > 0.f ? acc / W : 0.f);
   }
 }
 
@@ -431,20 +571,30 @@ static int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, const Dec
   const size_t smem = 1024 + static_cast<size_t>(C::NW) * C::NSTAGES * C::STAGE_BYTES +
                       C::NW * C::NSTAGES * sizeof(uint64_t) +
                       static_cast<size_t>(C::NW) * p.group * C::FIN_STRIDE * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(decode_attn_kernel<D, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
-        cudaSuccess)
+  if (smem + 64 > 227 * 1024) return kUnsupportedShape;       // static shared memory counts too
+  static size_t configured_by_device[64] = {};                // opt in to > 48 KB once per device and size
+  int dev = 0;
+  cudaGetDevice(&dev);
+  size_t& configured = configured_by_device[dev & 63];
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(decode_attn_kernel<D, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
       return kLaunchFailed;
-    configured = true;
+    configured = smem;
   }
-  if (smem > 227 * 1024) return kUnsupportedShape;
   dim3 grid(num_ctas, hkv / HPC);
   decode_attn_kernel<D, HPC><<<grid, C::NW * 32, smem, stream>>>(km, vm, p);
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
 }  // namespace mvb
+
+#ifdef MVB_DECODE_TRACE
+extern "C" int mvb_debug_set_decode_trace(void* ptr) {
+  unsigned long long* p = static_cast<unsigned long long*>(ptr);
+  return cudaMemcpyToSymbol(mvb::g_decode_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 extern "C" size_t mvb_decode_workspace_bytes(int max_seqs, int num_q_heads, int head_dim) {
   if (max_seqs <= 0 || num_q_heads <= 0 || head_dim <= 0) return 0;
@@ -474,7 +624,7 @@ extern "C" int mvb_decode_plan(const int32_t* cache_seqlens, int num_seqs, int w
   if (num_ctas > kMaxCtas) num_ctas = kMaxCtas;
   decode_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       cache_seqlens, num_seqs, window_left, cta_tokens_for(num_kv_heads, head_dim), num_ctas,
-      reinterpret_cast<DecodeHeader*>(ws), reinterpret_cast<int32_t*>(ws + l.first_seq),
+      num_seqs * num_q_heads, reinterpret_cast<DecodeHeader*>(ws), reinterpret_cast<CtaDesc*>(ws + l.descs),
       reinterpret_cast<int32_t*>(ws + l.tile_prefix));
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
@@ -492,7 +642,7 @@ extern "C" int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* 
   if (!decode_shape_ok(num_q_heads, num_kv_heads, head_dim)) return kUnsupportedShape;
   if (block_size % 16 != 0) return kUnsupportedShape;
   if (num_blocks * block_size > 0x7fffffffLL) return kUnsupportedShape;
-  if ((q_row_stride % 2) || (out_row_stride % 1) || !is_aligned(q, 4) || !is_aligned(out, 2)) return kMisaligned;
+  if ((q_row_stride % 2) || (out_row_stride % 4) || !is_aligned(q, 4) || !is_aligned(out, 8)) return kMisaligned;
   const DecodeLayout l = decode_layout(num_seqs, num_q_heads, head_dim);
   if (workspace_bytes < l.total || !is_aligned(workspace, 256)) return kInvalidArgument;
 
@@ -514,10 +664,11 @@ extern "C" int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window_left = window_left;
   p.hdr = reinterpret_cast<const DecodeHeader*>(ws);
-  p.first_seq = reinterpret_cast<const int32_t*>(ws + l.first_seq);
+  p.descs = reinterpret_cast<const CtaDesc*>(ws + l.descs);
   p.tile_prefix = reinterpret_cast<const int32_t*>(ws + l.tile_prefix);
   p.part_lse = reinterpret_cast<float*>(ws + l.lse);
   p.part_o = reinterpret_cast<float*>(ws + l.o);
+  p.arrivals = reinterpret_cast<int32_t*>(ws + l.tile_prefix) + num_seqs + 1;
   p.dev_status = dev_status;
 
   int num_ctas = sm_count();
@@ -536,7 +687,5 @@ extern "C" int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* 
     else if (hpc == 2) rc = launch_decode<256, 2>(km, vm, p, num_kv_heads, num_ctas, st);
     else if (hpc == 1) rc = launch_decode<256, 1>(km, vm, p, num_kv_heads, num_ctas, st);
   }
-  if (rc != kOk) return rc;
-  decode_combine_kernel<<<num_seqs, 256, 0, st>>>(p, head_dim);
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+  return rc;
 }

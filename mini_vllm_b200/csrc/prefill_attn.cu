@@ -348,8 +348,8 @@ static int launch_prefill(const CUtensorMap& qm, const CUtensorMap& km, const CU
 
 }  // namespace mvb
 
-extern "C" int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void* k, const void* v,
-                                int64_t kv_row_stride, int64_t kv_rows, const int32_t* cu_seqlens_q,
+extern "C" int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void* k, int64_t k_row_stride,
+                                const void* v, int64_t v_row_stride, int64_t kv_rows, const int32_t* cu_seqlens_q,
                                 const int32_t* cu_seqlens_k, const int32_t* block_table, int64_t table_stride,
                                 int block_size, int num_seqs, int total_q, int max_seqlen_q, int num_q_heads,
                                 int num_kv_heads, int head_dim, float scale, int window_left, void* out,
@@ -368,9 +368,9 @@ extern "C" int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void*
   CUtensorMap qm, km, vm;
   int rc = make_kv_tensor_map(&qm, q, total_q, num_q_heads, head_dim, q_row_stride, 128);
   if (rc != kOk) return rc;
-  rc = make_kv_tensor_map(&km, k, kv_rows, num_kv_heads, head_dim, kv_row_stride, bn);
+  rc = make_kv_tensor_map(&km, k, kv_rows, num_kv_heads, head_dim, k_row_stride, bn);
   if (rc != kOk) return rc;
-  rc = make_kv_tensor_map(&vm, v, kv_rows, num_kv_heads, head_dim, kv_row_stride, bn);
+  rc = make_kv_tensor_map(&vm, v, kv_rows, num_kv_heads, head_dim, v_row_stride, bn);
   if (rc != kOk) return rc;
 
   PrefillParams p;

@@ -21,8 +21,8 @@ class CudaGraphRunner:
         self.model = model
         self.config = config
         self.max_batch_size = min(max_batch_size, 256)
-        self.batch_size_list = [b for b in (1, 2, 4, 8) if b <= self.max_batch_size] + \
-            list(range(16, self.max_batch_size + 1, 16))
+        sizes = [b for b in (1, 2, 4, 8) if b <= self.max_batch_size] + list(range(16, self.max_batch_size + 1, 16))
+        self.batch_size_list = sorted(set(sizes + [self.max_batch_size]))   # the largest batch always has a graph
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.launches: dict[int, int] = {}       # library kernels inside each captured graph
         self.pool = None

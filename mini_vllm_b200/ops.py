@@ -185,7 +185,7 @@ def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, c
         block_table.stride(0), block_table.shape[1], B, hq, hkv, d, float(scale), window_left, _ptr(out),
         out.stride(0), _ptr(workspace), workspace.numel(), _ptr(status), _stream())
     _cabi.check(rc, "mvb_decode_attn")
-    LaunchCounter.add(2)
+    LaunchCounter.add(1)
     return out
 
 
@@ -199,17 +199,16 @@ def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q
     Tq, hq, d = q.shape
     if block_table is None:
         _heads_contiguous(k, "k"); _heads_contiguous(v, "v")
-        assert k.stride(0) == v.stride(0), "k and v must share a row stride"
-        kv_rows, hkv, kv_stride, bs, tstride = k.shape[0], k.shape[1], k.stride(0), 0, 0
+        kv_rows, hkv, k_stride, v_stride, bs, tstride = k.shape[0], k.shape[1], k.stride(0), v.stride(0), 0, 0
     else:
         _need(block_table, torch.int32, "block_table")
         assert k.dim() == 4 and k.is_contiguous() and v.is_contiguous()
         nblk, bs, hkv, _ = k.shape
-        kv_rows, kv_stride, tstride = nblk * bs, hkv * d, block_table.stride(0)
+        kv_rows, k_stride, v_stride, tstride = nblk * bs, hkv * d, hkv * d, block_table.stride(0)
     if out is None:
         out = torch.empty(Tq, hq, d, dtype=torch.bfloat16, device=q.device)
     rc = _cabi.load().mvb_prefill_attn(
-        _ptr(q), q.stride(0), _ptr(k), _ptr(v), kv_stride, kv_rows, _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
+        _ptr(q), q.stride(0), _ptr(k), k_stride, _ptr(v), v_stride, kv_rows, _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
         _ptr(block_table), tstride, bs, cu_seqlens_q.numel() - 1, Tq, int(max_seqlen_q), hq, hkv, d, float(scale),
         window_left, _ptr(out), out.stride(0), _ptr(status), _stream())
     _cabi.check(rc, "mvb_prefill_attn")

@@ -104,6 +104,9 @@ class OracleExecutor:
         self.model, self.block_size = model, block_size
 
     def execute(self, batch) -> list[int]:
+        return torch.argmax(self.logits(batch), dim=-1).tolist()        # sampler.py:31
+
+    def logits(self, batch) -> torch.Tensor:
         from . import packing
         dev = self.model.device
         reqs = batch.requests
@@ -116,8 +119,7 @@ class OracleExecutor:
         ctx = {"prefill": batch.type == 0, "slot_mapping": t(p["slot_mapping"]), "block_table": t(p["block_table"]),
                "cu_seqlens_q": t(p.get("cu_seqlens_q")), "cu_seqlens_k": t(p.get("cu_seqlens_k")),
                "cache_seqlens": t(p.get("cache_seqlens"))}
-        logits = self.model.forward(ctx, t(p["input_ids"]), t(p["positions"]))
-        return torch.argmax(logits, dim=-1).tolist()                    # sampler.py:31
+        return self.model.forward(ctx, t(p["input_ids"]), t(p["positions"]))
 
 
 def reference_names(state: dict, family: str, cfg) -> dict:

@@ -27,30 +27,45 @@ def small_gemma3(**kw):
                         sliding_window=64, query_pre_attn_scalar=256, **kw)
 
 
-def oracle_generate(engine: Engine, family: str, prompts, params, sched_cfg):
-    """Re-run the same workload with the oracle model under an identical scheduler."""
+def oracle_replay(engine: Engine, family: str, prompts, params, sched_cfg, got):
+    """Teacher-forced check: the oracle model follows the product's token stream under an identical
+    scheduler and scores every token the product chose.
+
+    Returns (steps, exact, worst_deficit): the number of sampled tokens, how many equal the oracle's
+    own argmax, and the largest amount by which a chosen token's oracle logit fell short of the
+    oracle's maximum.  bf16 logits of magnitude ~2 carry ~1e-2 of rounding noise, so near-ties can
+    flip; anything beyond a few ulps is a real error.
+    """
     cfg = engine.config
-    weights = reference_names({k: v.detach() for k, v in engine.executor.model.state_dict().items()
-                               if "cos_sin" not in k and "embed_scale" not in k}, family, cfg.hf_config)
+    weights = reference_names({k: v.detach() for k, v in engine.executor.model.state_dict().items()},
+                              family, cfg.hf_config)
     model = OracleModel(weights, cfg.hf_config, family, cfg.kv_cache_num_blocks, cfg.kv_cache_block_size,
                         device=engine.executor.device)
     ex, sch = OracleExecutor(model, cfg.kv_cache_block_size), Scheduler(sched_cfg)
     reqs = [Request(p, sp) for p, sp in zip(prompts, params)]
+    index = {r.id: i for i, r in enumerate(reqs)}
     for r in reqs:
         sch.submit(r)
-    margins = {}
+    steps = exact = 0
+    worst = 0.0
     while not sch.finished:
         batch = sch.schedule()
-        sch.update(batch, ex.execute(batch))
-    return [r.completion_tokens for r in reqs]
+        logits = ex.logits(batch).float()
+        forced = [got[index[r.id]][r.num_completion_tokens] for r in batch.requests]
+        chosen = logits[torch.arange(len(forced)), torch.tensor(forced, device=logits.device)]
+        top = logits.max(dim=-1).values
+        worst = max(worst, ((top - chosen) / top.abs().clamp_min(1.0)).max().item())
+        exact += int((logits.argmax(-1).cpu() == torch.tensor(forced)).sum())
+        steps += len(forced)
+        sch.update(batch, forced)
+    return steps, exact, worst
 
 
-def check_tokens(got, want, min_exact=0.9):
-    """Identical ids expected; a divergence is tolerated only as a rare bf16 near-tie."""
-    exact = sum(g == w for g, w in zip(got, want))
-    first_bad = [next(i for i, (a, b) in enumerate(zip(g, w)) if a != b) for g, w in zip(got, want) if g != w]
-    assert exact >= min_exact * len(want), f"only {exact}/{len(want)} sequences identical; first mismatches at {first_bad}"
-    return exact
+def check_tokens(engine, family, prompts, params, cfg, got):
+    steps, exact, worst = oracle_replay(engine, family, prompts, params, cfg, got)
+    assert worst <= 4 * 2 ** -8, f"a chosen token is {worst:.4f} (relative) below the oracle's best logit"
+    assert exact >= 0.95 * steps, f"only {exact}/{steps} tokens equal the oracle argmax"
+    return exact, steps
 
 
 @pytest.mark.parametrize("family,shape,graphs", [("qwen3", small_qwen3, True), ("qwen3", small_qwen3, False),
@@ -67,8 +82,7 @@ def test_greedy_tokens_match_oracle(cuda, family, shape, graphs):
     engine.executor.check_device_status()
     got = [o["tokens"] for o in out]
     assert all(len(t) == 40 for t in got)
-    want = oracle_generate(engine, family, prompts, params, cfg)
-    check_tokens(got, want)
+    check_tokens(engine, family, prompts, params, cfg, got)
 
 
 def test_prefix_cache_and_preemption_match_oracle(cuda):
@@ -86,8 +100,7 @@ def test_prefix_cache_and_preemption_match_oracle(cuda):
     out = engine.generate(prompts, copy.deepcopy(params), use_tqdm=False)
     engine.executor.check_device_status()
     got = [o["tokens"] for o in out]
-    want = oracle_generate(engine, "qwen3", prompts, params, cfg)
-    check_tokens(got, want)
+    check_tokens(engine, "qwen3", prompts, params, cfg, got)
 
 
 def test_sampling_params_paths(cuda):
