@@ -249,16 +249,16 @@ def cpu_reference_sample(budget_s: float = 20.0, seed: int = 0):
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     hf = qwen3_shape()
-    cfg = Config(hf_config=hf, kv_cache_num_blocks=16, max_num_batched_seqs=4, use_cuda_graph=False, seed=seed)
+    cfg = Config(hf_config=hf, kv_cache_num_blocks=40, max_num_batched_seqs=8, use_cuda_graph=False, seed=seed)
     model = load_model(cfg, device="cpu")
     weights = reference_names(dict(model.state_dict()), "qwen3", hf)
     del model
-    omodel = OracleModel(weights, hf, "qwen3", 16, 256, device="cpu")
+    omodel = OracleModel(weights, hf, "qwen3", 40, 256, device="cpu")
     ex = OracleExecutor(omodel, 256)
-    reqs = config2_requests(seed)[:2]
-    n_req, n_dec = 2, 4
+    n_req, n_dec = 8, 48
+    reqs = config2_requests(seed)[:n_req]
     sch = Scheduler(cfg)
-    rs = [Request(r.prompt[:256], SamplingParams(max_tokens=n_dec, ignore_eos=True)) for r in reqs[:n_req]]
+    rs = [Request(r.prompt, SamplingParams(max_tokens=n_dec, ignore_eos=True)) for r in reqs]
     for r in rs:
         sch.submit(r)
     t0 = time.perf_counter()
@@ -269,7 +269,8 @@ def cpu_reference_sample(budget_s: float = 20.0, seed: int = 0):
         tokens += sum(len(r.tokens) - r.num_cached_tokens for r in batch.requests) if batch.type == 0 else len(out)
         sch.update(batch, out)
     dt = time.perf_counter() - t0
-    sample = f"{n_req} requests, prompts cut to <=256 tokens, {n_dec} generated tokens each, bf16 weights, per-token extrapolation"
+    sample = (f"first {n_req} requests of the workload, full prompts, {n_dec} generated tokens each, bf16 weights, "
+              "prefill+decode tokens / wall time (per-token extrapolation)")
     return tokens / dt, threads, sample, dt
 
 
