@@ -36,7 +36,8 @@ enum mvb_status {
   MVB_LAUNCH_FAILED = -3,
   MVB_TENSOR_MAP_FAILED = -4,
   MVB_MISALIGNED = -5,
-  MVB_NO_DRIVER_ENTRY = -6
+  MVB_NO_DRIVER_ENTRY = -6,
+  MVB_SCRATCH_TOO_SMALL = -7
 };
 
 /* Library ABI version (bumped when a signature changes). */
@@ -128,6 +129,35 @@ int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, co
                     int num_q_heads, int num_kv_heads, int head_dim, float scale, int window_left, void* out,
                     int64_t out_row_stride, void* workspace, size_t workspace_bytes, int32_t* dev_status,
                     void* stream);
+
+/*
+ * Decode attention for callers that cannot provide a workspace.  (No counterpart in the reference,
+ * which lets PyTorch allocate whatever its attention library needs.)
+ *
+ * Meant for users who must not, or cannot, allocate device memory around this call: a process whose
+ * GPU memory is fully parcelled out at start-up, a thin binding that can only pass on buffers it was
+ * given, or a latency-critical loop that has to stay clear of cudaMalloc and its device-wide
+ * synchronisation.  It computes exactly what mvb_decode_plan followed by mvb_decode_attn compute, but
+ * keeps the plan, the partial results and the arrival counters in a MVB_STATIC_SCRATCH_BYTES array
+ * that is part of the library image: each GPU that loads the library holds that memory until the
+ * process ends.  Inputs and outputs are still the caller's.
+ *
+ *   - Limit: the scratch needed for (num_seqs, num_q_heads, head_dim) must fit the 8 MiB array.
+ *     That covers 16 or 32 query heads of dimension 128 (or 4 to 16 of dimension 256) with
+ *     thousands of sequences; 64 heads x 128 does not fit.  Larger requests return
+ *     MVB_SCRATCH_TOO_SMALL and launch nothing.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     outside any stream capture.  No call allocates or frees memory.
+ *   - All calls on a device share the one array.  Each call re-plans and clears what has to start
+ *     at zero, so earlier contents do not matter, but two calls whose kernels overlap on the GPU
+ *     (different streams) would race on it: keep them ordered.
+ */
+#define MVB_STATIC_SCRATCH_BYTES (8u << 20)
+int mvb_decode_attn_static(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                           int64_t num_blocks, int block_size, const int32_t* cache_seqlens,
+                           const int32_t* block_table, int64_t table_stride, int table_width, int num_seqs,
+                           int num_q_heads, int num_kv_heads, int head_dim, float scale, int window_left,
+                           void* out, int64_t out_row_stride, int32_t* dev_status, void* stream);
 
 /*
  * Causal varlen prefill attention on the tcgen05 tensor cores.

@@ -23,6 +23,8 @@ SIGNATURES = {
     "mvb_decode_plan": (i32, [vp, i32, i32, i32, i32, i32, vp, sz, vp]),
     "mvb_decode_attn": (i32, [vp, i64, vp, vp, i64, i32, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, vp, i64,
                               vp, sz, vp, vp]),
+    "mvb_decode_attn_static": (i32, [vp, i64, vp, vp, i64, i32, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, vp,
+                                     i64, vp, vp]),
     "mvb_prefill_attn": (i32, [vp, i64, vp, i64, vp, i64, i64, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, f32,
                                i32, vp, i64, vp, vp]),
     "mvb_sample": (i32, [vp, i64, i32, i32, vp, vp, u64, u64, vp, vp, vp]),

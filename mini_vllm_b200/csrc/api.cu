@@ -13,6 +13,7 @@ extern "C" const char* mvb_status_string(int status) {
     case MVB_TENSOR_MAP_FAILED: return "tensor map encoding failed";
     case MVB_MISALIGNED: return "pointer or stride not aligned";
     case MVB_NO_DRIVER_ENTRY: return "cuTensorMapEncodeTiled not available from the driver";
+    case MVB_SCRATCH_TOO_SMALL: return "request needs more than the built-in 8 MiB decode scratch";
     default: return "unknown status";
   }
 }

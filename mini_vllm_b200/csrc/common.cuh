@@ -19,6 +19,7 @@ enum Status : int {
   kTensorMapFailed = -4,
   kMisaligned = -5,
   kNoDriverEntry = -6,
+  kScratchTooSmall = -7,
 };
 
 // ---- device-detected error codes written to dev_status[0] (first error wins) ----------------

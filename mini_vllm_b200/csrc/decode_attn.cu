@@ -27,6 +27,8 @@
 #include "mini_vllm_b200.h"
 #include "scan.cuh"
 
+#include <mutex>
+
 namespace mvb {
 
 // Optional timeline probe (compiled in only with -DMVB_DECODE_TRACE): thread 0 of every CTA stamps
@@ -688,4 +690,58 @@ extern "C" int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* 
     else if (hpc == 1) rc = launch_decode<256, 1>(km, vm, p, num_kv_heads, num_ctas, st);
   }
   return rc;
+}
+
+// ---- decode attention without caller-supplied scratch ------------------------------------------------
+// Some users of this library cannot hand it a workspace: a serving process whose device memory is
+// carved up once at start-up and that has no allocator to ask afterwards, a binding from a runtime
+// that only passes through the tensors it already owns, or a latency-critical loop that must never
+// reach cudaMalloc (which synchronises the whole device).  For them the plan, the partial results
+// and the arrival counters live in the array below, which is part of the loaded module: every GPU
+// that loads the library holds these 8 MiB until the process exits.
+namespace mvb {
+
+constexpr size_t kStaticScratchBytes = MVB_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticScratchBytes];
+
+// In host code the array's name only identifies the symbol; the kernels need its address in device
+// memory, which differs per device.  Looked up once per device, with that device current.
+static int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* addr_by_device[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kLaunchFailed;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr_by_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_decode_scratch) != cudaSuccess || ptr == nullptr) return kLaunchFailed;
+    addr_by_device[dev] = ptr;
+  }
+  *out = addr_by_device[dev];
+  return kOk;
+}
+
+}  // namespace mvb
+
+extern "C" int mvb_decode_attn_static(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                                      int64_t num_blocks, int block_size, const int32_t* cache_seqlens,
+                                      const int32_t* block_table, int64_t table_stride, int table_width,
+                                      int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                                      int window_left, void* out, int64_t out_row_stride, int32_t* dev_status,
+                                      void* stream) {
+  using namespace mvb;
+  if (num_seqs <= 0 || num_q_heads <= 0 || head_dim <= 0) return kInvalidArgument;
+  if (!decode_shape_ok(num_q_heads, num_kv_heads, head_dim)) return kUnsupportedShape;
+  if (decode_layout(num_seqs, num_q_heads, head_dim).total > kStaticScratchBytes) return kScratchTooSmall;
+  void* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc != kOk) return rc;
+  // The plan launch rewrites the descriptors and zeroes the arrival counters, so nothing left in
+  // the array by an earlier call is read.
+  rc = mvb_decode_plan(cache_seqlens, num_seqs, window_left, num_q_heads, num_kv_heads, head_dim, scratch,
+                       kStaticScratchBytes, stream);
+  if (rc != kOk) return rc;
+  return mvb_decode_attn(q, q_row_stride, k_cache, v_cache, num_blocks, block_size, cache_seqlens, block_table,
+                         table_stride, table_width, num_seqs, num_q_heads, num_kv_heads, head_dim, scale,
+                         window_left, out, out_row_stride, scratch, kStaticScratchBytes, dev_status, stream);
 }

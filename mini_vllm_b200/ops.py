@@ -189,6 +189,32 @@ def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, c
     return out
 
 
+def decode_attn_static(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_seqlens: torch.Tensor,
+                       block_table: torch.Tensor, scale: float, window_left: int, out: torch.Tensor,
+                       status: torch.Tensor | None = None) -> torch.Tensor:
+    """Decode attention that brings its own scratch (``mvb_decode_attn_static``).
+
+    For callers that have no way to allocate a workspace next to this call: the plan and the partial
+    results live in an 8 MiB array inside the library, so the only buffers involved are the ones passed
+    here, ``out`` included.  Calls on one device share that array and must not overlap on the GPU;
+    the first call on a device should happen outside stream capture.  Raises ``KernelError`` when the
+    request is too large for the built-in array.
+    """
+    _need(q, torch.bfloat16, "q"); _heads_contiguous(q, "q")
+    _need(cache_seqlens, torch.int32, "cache_seqlens"); _need(block_table, torch.int32, "block_table")
+    _need(out, torch.bfloat16, "out")
+    B, hq, d = q.shape
+    nblk, bs, hkv, _ = k_cache.shape
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and block_table.stride(1) == 1
+    rc = _cabi.load().mvb_decode_attn_static(
+        _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), nblk, bs, _ptr(cache_seqlens), _ptr(block_table),
+        block_table.stride(0), block_table.shape[1], B, hq, hkv, d, float(scale), window_left, _ptr(out),
+        out.stride(0), _ptr(status), _stream())
+    _cabi.check(rc, "mvb_decode_attn_static")
+    LaunchCounter.add(2)
+    return out
+
+
 def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
                  cu_seqlens_k: torch.Tensor, max_seqlen_q: int, scale: float, window_left: int = -1,
                  block_table: torch.Tensor | None = None, out: torch.Tensor | None = None,
