@@ -1,0 +1,58 @@
+"""The shared library loads on a machine without a GPU and exports every function the header declares."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from mini_vllm_b200 import _cabi
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "mini_vllm_b200.h"
+
+
+def declared_functions() -> list[str]:
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(mvb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_functions()
+    for must in ("mvb_pack_prefill", "mvb_pack_decode", "mvb_rope_kv_write", "mvb_decode_plan", "mvb_decode_attn",
+                 "mvb_decode_attn_static", "mvb_prefill_attn", "mvb_sample", "mvb_decode_workspace_bytes"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol_and_binding_covers_them():
+    lib = _cabi.load()
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+        assert name in _cabi.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(_cabi.SIGNATURES) == set(declared_functions())
+
+
+def test_host_only_calls_work_without_a_gpu():
+    lib = _cabi.load()
+    assert lib.mvb_abi_version() == 1
+    assert lib.mvb_status_string(0) == b"ok"
+    assert b"scratch" in lib.mvb_status_string(-7)
+    assert lib.mvb_decode_workspace_bytes(512, 16, 128) > 2 * 160 * 16 * 128 * 4
+    assert lib.mvb_decode_workspace_bytes(0, 16, 128) == 0
+    # argument errors are caught on the host before anything is launched
+    assert lib.mvb_rope_kv_write(None, 0, None, 0, None, 0, None, None, 0, None, None, None, 0, 4, 2, 2, 100, 0,
+                                 None, None) == -2          # head_dim not a multiple of 16
+    assert lib.mvb_sample(None, 0, 1, 10, None, None, 0, 0, None, None, None) == -1
+    assert lib.mvb_decode_plan(None, 1, -1, 16, 8, 128, None, 0, None) == -1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_cabi, "_lib", None)
+    monkeypatch.setattr(_cabi, "_LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(_cabi.KernelError, match="no CPU or PyTorch fallback"):
+        _cabi.load()
+
+
+def test_ops_reject_cpu_tensors():
+    import torch
+    from mini_vllm_b200 import ops
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        ops.sample(torch.zeros(2, 16, dtype=torch.bfloat16))
