@@ -24,6 +24,8 @@
 #include "host_util.cuh"
 #include "mini_vllm_b200.h"
 
+#include <type_traits>
+
 namespace mvb {
 
 // Optional phase timers (only with -DMVB_PREFILL_TRACE): one CTA accumulates SM-clock deltas per
@@ -211,9 +213,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         if (ok && it >= 2) ok = wait(B_VFREE + st, ((it >> 1) - 1) & 1, 200 + it);
         if (ok) load_tile(&v_map, v_s + st * C::KV_BYTES, &bars[B_VFULL + st], z);
         MVB_PTRACE(0, it, 1);
-#if defined(MVB_PREFILL_VARIANT) && MVB_PREFILL_VARIANT == 5
-        if (ok) { wait(B_VFULL + st, (it >> 1) & 1, 999); MVB_PTRACE(0, it, 2); }   // measures the V load latency
-#endif
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       const int valid = k_len - j * BN;
@@ -237,14 +236,23 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     if (lane == 0) { MVB_PT_FLUSH(0); }
   } else if (warp == NQ * 4 + 1) {
     // ============================ MMA warp (one issuing thread) ======================================
+    // This thread shares its scheduler with two softmax warps that always have work, so every
+    // instruction between two tcgen05.mma costs tensor-pipe time: ranges are scalars, tile indices
+    // are compile-time constants and a wait is one try_wait unless the barrier is really not ready.
     if (lane == 0) {
       bool ok = true;
       MVB_PT_DECL
-      // descriptors differ from step to step only in their start address (low 14 bits, 16-byte units)
       const uint64_t q_desc0 = umma_desc_sw128(q_s, 16, 1024);
       const uint64_t k_desc0 = umma_desc_sw128(k_s, 16, 1024);
       const uint64_t v_desc0 = umma_desc_sw128(v_s, C::HALF_KV, 1024);
-      auto issue_s = [&](int t, int st) {                     // S_t = Q_t . K^T
+      const int jlo0 = jlo_t[0], jhi0 = jhi_t[0];
+      const int jlo1 = jlo_t[NQ - 1], jhi1 = jhi_t[NQ - 1];   // tile NQ-1 (== tile 0 when NQ == 1)
+      const int j_partial = k_len / BN;                       // first KV tile with rows past the end
+      auto ready = [&](int slot, uint32_t parity, int where) -> bool {
+        return mbar_try_wait(&bars[slot], parity) ? true : wait(slot, parity, where);
+      };
+      auto issue_s = [&](auto tt, int st) {                   // S_t = Q_t . K^T
+        constexpr int t = decltype(tt)::value;
         const uint64_t qd = q_desc0 + ((t * C::Q_BYTES) >> 4), kd = k_desc0 + ((st * C::KV_BYTES) >> 4);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
@@ -253,65 +261,77 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         }
         umma_commit(&bars[B_SFULL + t]);
       };
-      // O_t (+)= P_t . V for the 64 keys of half h; P_t from tensor memory
-      auto issue_pv_half = [&](int t, int st, int h, bool first) {
-        const uint64_t vd = v_desc0 + ((st * C::KV_BYTES) >> 4);
-#pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {
-          const int ks = h * 4 + k4;
-          umma_bf16_ts(tmem + C::O_COL + t * D, tmem + C::S_COL + t * BN + ks * 8, vd + ((ks * 2048) >> 4), IDESC_O,
-                       (!first || ks > 0) ? 1u : 0u);
-        }
-      };
-      // PV of tile t for KV tile j: needs V (fixed up if partial) and the halves of P_t as they arrive
-      auto pv_step = [&](int t, int it) {
+      // O_t (+)= P_t . V for KV tile j: V must have landed (and been fixed up if partial); the halves
+      // of P_t are consumed as the softmax group publishes them
+      auto pv_step = [&](auto tt, int it, bool v_known) {
+        constexpr int t = decltype(tt)::value;
         const int st = it & 1, j = j_lo + it;
-        if (!active(t, j)) return;
-        ok = ok && wait(B_VFULL + st, (it >> 1) & 1, 400 + it);
-        if (ok && k_len - j * BN < BN) ok = wait(B_VFIXED, 0, 450);
+        const int jlo = t == 0 ? jlo0 : jlo1;
+        if (!v_known) {
+          ok = ready(B_VFULL + st, (it >> 1) & 1, 400 + it);
+          if (ok && j >= j_partial) ok = ready(B_VFIXED, 0, 450);
+        }
         MVB_PTRACE(1, it, 6);
+        const uint64_t vd = v_desc0 + ((st * C::KV_BYTES) >> 4);
+        const uint32_t first = (j == jlo) ? 0u : 1u;
 #pragma unroll
         for (int h = 0; h < BN / 64; ++h) {
-          ok = ok && wait(B_PFULL + 2 * t + h, (j - jlo_t[t]) & 1, 500 + it);
+          if (ok) ok = ready(B_PFULL + 2 * t + h, (j - jlo) & 1, 500 + it);
           if (!ok) return;
           tc_fence_after();
           MVB_PTRACE(1, it, 7);
-          issue_pv_half(t, st, h, j == jlo_t[t]);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const int ks = h * 4 + k4;
+            umma_bf16_ts(tmem + C::O_COL + t * D, tmem + C::S_COL + t * BN + ks * 8, vd + ((ks * 2048) >> 4), IDESC_O,
+                         ks > 0 ? 1u : first);
+          }
           MVB_PTRACE(1, it, (t == 0 ? 5 : 3));
         }
         umma_commit(&bars[B_ODONE + t]);
       };
+      using T0 = std::integral_constant<int, 0>;
+      using T1 = std::integral_constant<int, NQ - 1>;
+      bool prev_a0 = false, prev_a1 = false;                  // was tile 0 / tile NQ-1 active in the previous step
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it & 1, j = j_lo + it;
         MVB_PTRACE(1, it, 0);
-        ok = wait(B_KFULL + st, (it >> 1) & 1, 600 + it);
+        ok = ready(B_KFULL + st, (it >> 1) & 1, 600 + it);
         if (!ok) break;
         tc_fence_after();
         MVB_PTRACE(1, it, 1);
+        const bool a0 = j >= jlo0 && j <= jhi0;
         // interleave the tiles: S0(j), PV1(j-1), S1(j), PV0(j)
-        if (active(0, j)) {
-          if (j == jlo_t[0]) ok = wait(B_QFULL + 0, 0, 610);
-          if (ok) issue_s(0, st);
+        if (a0) {
+          if (j == jlo0) ok = ready(B_QFULL + 0, 0, 610);
+          if (ok) issue_s(T0{}, st);
         }
         MVB_PTRACE(1, it, 2);
-        if (NQ > 1 && it >= 1 && ok) {
-          pv_step(NQ - 1, it - 1);
-          if (ok) umma_commit(&bars[B_VFREE + ((it - 1) & 1)]);
-        }
-        MVB_PTRACE(1, it, 3);
-        if (NQ > 1 && ok && active(NQ - 1, j)) {
-          if (j == jlo_t[NQ - 1]) ok = wait(B_QFULL + NQ - 1, 0, 611);
-          if (ok) issue_s(NQ - 1, st);
+        if constexpr (NQ > 1) {
+          if (it >= 1 && ok) {
+            if (prev_a1) pv_step(T1{}, it - 1, prev_a0);      // tile 0's PV already waited for that V tile
+            if (ok) umma_commit(&bars[B_VFREE + ((it - 1) & 1)]);
+          }
+          MVB_PTRACE(1, it, 3);
+          const bool a1 = rows_t[NQ - 1] > 0 && j >= jlo1 && j <= jhi1;
+          if (ok && a1) {
+            if (j == jlo1) ok = ready(B_QFULL + NQ - 1, 0, 611);
+            if (ok) issue_s(T1{}, st);
+          }
+          prev_a1 = a1;
         }
         if (ok) umma_commit(&bars[B_KFREE + st]);
         MVB_PTRACE(1, it, 4);
-        if (ok) pv_step(0, it);
+        if (ok && a0) pv_step(T0{}, it, false);
         MVB_PTRACE(1, it, 5);
         if (NQ == 1 && ok) umma_commit(&bars[B_VFREE + st]);
+        prev_a0 = a0;
       }
-      if (NQ > 1 && ok) {
-        pv_step(NQ - 1, n_it - 1);
-        if (ok) umma_commit(&bars[B_VFREE + ((n_it - 1) & 1)]);
+      if constexpr (NQ > 1) {
+        if (ok) {
+          if (prev_a1) pv_step(T1{}, n_it - 1, prev_a0);
+          if (ok) umma_commit(&bars[B_VFREE + ((n_it - 1) & 1)]);
+        }
       }
       MVB_PT_FLUSH(1);
     }
