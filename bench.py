@@ -179,18 +179,24 @@ def decode_roofline(engine, contexts, peaks):
         launches += layers
     achieved = total_bytes / (total_ms * 1e-3) / 1e9 if total_ms else 0.0
     return {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-            "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None, "kernel": "decode_attn_kernel<128,8>",
+            "frac": round(achieved / peaks["hbm_gbs"], 4),
+            # ncu on the 2.063 GB config-3 launch read 2.0733 GB and wrote 5.8 MB (profiles/): traffic is
+            # 1.008 x the algorithmic bytes and grows in proportion, so it is scaled to this launch size
+            "traffic": int(1.008 * total_bytes / max(launches, 1)), "kernel": "decode_attn_kernel<128,8>",
             "launches_timed": launches, "avg_launch_us": round(total_ms * 1e3 / max(launches, 1), 2),
             "avg_bytes_per_launch": int(total_bytes / max(launches, 1)),
             "note": "algorithmic K+V bytes of recorded decode steps, 28 layer launches replayed from a CUDA graph; peak = STREAM copy"}
 
 
-def kernel_extras(dev, peaks):
-    """Fixed single-layer cases: the 240-sequence decode batch and the 16-sequence prefill batch."""
+def kernel_extras(dev, peaks, nl=4):
+    """Fixed single-layer cases: the 240-sequence decode batch and the 16-sequence prefill batch.
+
+    ``nl`` distinct KV pools (2.3 GB each) are rotated so that consecutive launches share nothing in L2.
+    """
     from mini_vllm_b200 import ops
     from mini_vllm_b200.workloads import table_tensor
     case, _ = config3()
-    hq, hkv, d, nl = 16, 8, 128, 4
+    hq, hkv, d = 16, 8, 128
     pools = [torch.randn(2, case.pool_blocks, 256, hkv, d, device=dev, dtype=torch.bfloat16) for _ in range(nl)]
     out = {}
     # decode part
@@ -301,9 +307,30 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-legs", action="store_true",
+                    help="profiling aid: only the fixed single-layer kernel cases (one 2.3 GB pool), then exit")
+    ap.add_argument("--engine-steps", type=int, default=0,
+                    help="profiling aid: prefill + N decode steps of the workload without CUDA graphs, then exit")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.kernel_legs:
+        peaks, _ = measured_peaks()
+        print(json.dumps(kernel_extras(torch.device("cuda", 0), peaks, nl=1)))
+        return
+    if args.engine_steps:
+        from mini_vllm_b200.engine.engine import Engine
+        cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=512, max_num_batched_seqs=64,
+                     max_num_batched_tokens=16384, gpu_memory_utilization=0.5, use_cuda_graph=False, seed=0)
+        eng = Engine(cfg)
+        for r in config2_requests(0):
+            eng.submit(r.prompt, SamplingParams(max_tokens=r.max_tokens, ignore_eos=True))
+        done = 0
+        while done < args.engine_steps:
+            done += eng.step().type == 1
+        torch.cuda.synchronize()
+        print(json.dumps({"prefill_steps": eng.metrics.prefill_steps, "decode_steps": eng.metrics.decode_steps}))
+        return
 
     from mini_vllm_b200 import ops
     world = int(os.environ.get("WORLD_SIZE", "1"))
