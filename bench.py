@@ -11,9 +11,11 @@ path); the global request list of 64*N requests is partitioned by the host dispa
 count, so per-GPU work is fixed: weak scaling.
 
 Metric: prompt+generated tokens per second, whole job, all GPUs.
-* ``value``: the job timed with CUDA events.
-* ``e2e``: the same job through ``Engine.generate`` with host token lists in and out (wall clock,
-  uploads and result reads inside the timed region).
+* ``value``: the job's device time, CUDA events around its first and last kernel (the engine's step loop
+  is pipelined: sampled ids stay in HBM and feed the next step's packing kernel).
+* ``e2e``: the same job through ``Engine.generate`` with host token lists in and out (wall clock:
+  request submission, every step's metadata upload, every step's token read-back and the final list
+  assembly are inside the timed region).
 * ``roofline``: decode attention kernel, the largest kernel of the step: K/V bytes of the contexts
   it read / CUDA-event time, replayed on contexts recorded during the job, against the measured
   HBM copy bandwidth.  ``kernels`` adds the same figure on the fixed 240-sequence decode batch
@@ -39,6 +41,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 from mini_vllm_b200.config import Config, SamplingParams, qwen3_shape  # noqa: E402
+from mini_vllm_b200.dispatcher import partition_by_tokens  # noqa: E402
 from mini_vllm_b200.workloads import (QWEN3_0P6B, config2_requests, config3, decode_kv_bytes,  # noqa: E402
                                        prefill_flops)
 
@@ -51,17 +54,6 @@ def measured_peaks() -> tuple[dict, str]:
     if p.exists():
         return json.loads(p.read_text()), "measured"
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
-
-
-def partition_by_tokens(requests, n_parts: int):
-    """Host dispatcher: longest first, each request to the replica with the fewest tokens so far."""
-    order = sorted(range(len(requests)), key=lambda i: -(len(requests[i].prompt) + requests[i].max_tokens))
-    loads, parts = [0] * n_parts, [[] for _ in range(n_parts)]
-    for i in order:
-        j = min(range(n_parts), key=lambda r: (loads[r], r))
-        parts[j].append(i)
-        loads[j] += len(requests[i].prompt) + requests[i].max_tokens
-    return [sorted(p) for p in parts]
 
 
 class ClockSampler:
@@ -115,15 +107,17 @@ def run_job(engine, reqs, record_contexts=None):
     params = [SamplingParams(max_tokens=r.max_tokens, ignore_eos=True) for r in reqs]
     ex = engine.executor
     if record_contexts is not None:
-        orig = ex._build_decode_input
+        orig = ex.launch
         count = [0]
 
-        def spy(requests):
-            if count[0] % 40 == 20:
-                record_contexts.append(([len(r.tokens) for r in requests], [list(r.blocks) for r in requests]))
-            count[0] += 1
-            return orig(requests)
-        ex._build_decode_input = spy
+        def spy(batch, slots):
+            if batch.type == 1:
+                if count[0] % 40 == 20:
+                    record_contexts.append(([len(r.tokens) for r in batch.requests],
+                                            [list(r.blocks) for r in batch.requests]))
+                count[0] += 1
+            return orig(batch, slots)
+        ex.launch = spy
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
@@ -133,10 +127,10 @@ def run_job(engine, reqs, record_contexts=None):
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
     if record_contexts is not None:
-        ex._build_decode_input = orig
+        ex.launch = orig
     n_tok = sum(len(p) for p in prompts) + sum(len(o["tokens"]) for o in out)
     assert all(len(o["tokens"]) == r.max_tokens for o, r in zip(out, reqs))
-    return n_tok, wall, e0.elapsed_time(e1)
+    return n_tok, wall, engine.last_job_device_ms
 
 
 def decode_roofline(engine, contexts, peaks):
@@ -344,7 +338,7 @@ def main():
     peaks, peak_kind = measured_peaks()
 
     all_reqs = config2_requests(seed=0, n=64 * world)
-    mine = [all_reqs[i] for i in partition_by_tokens(all_reqs, world)[rank]]
+    mine = [all_reqs[i] for i in partition_by_tokens([len(r.prompt) + r.max_tokens for r in all_reqs], world)[rank]]
     engine = build_engine(local_rank)
     dev = engine.executor.device
 

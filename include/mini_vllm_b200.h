@@ -104,6 +104,27 @@ int mvb_rope_kv_write(void* q, int64_t q_row_stride, void* k, int64_t k_row_stri
                       int32_t* dev_status, void* stream);
 
 /*
+ * Per-head RMSNorm of q and k + rotary embedding + paged KV-cache write in one kernel.
+ * Replaces the q_norm / k_norm / rotary_embedding / store_kvcache sequence of the model call-sites
+ * (minivllm/models/models/qwen3.py:89-94, minivllm/models/models/gemma3.py:97-102).
+ *   q, k, v are read where the projection left them (views of the packed qkv output are fine: only
+ *   the row strides matter).  Each head row is normalised in fp32,
+ *     y = x * rsqrt(mean(x^2) + eps) * w          (unit_offset == 0, nn.RMSNorm, qwen3.py:64-65)
+ *     y = x * rsqrt(mean(x^2) + eps) * (1 + w)    (unit_offset != 0, gemma3.py:12-24)
+ *   rounded to bf16 as the stand-alone norm would, rotated like mvb_rope_kv_write, and written: q in
+ *   place, k to the cache slot (and in place if k_in_place), v to the cache slot.
+ *   q_weight, k_weight: bf16 [head_dim].  head_dim / 16 must be a power of two (<= 32).
+ * Results equal the unfused sequence up to the summation order of the squares (at most one bf16 ulp
+ * on a few elements); use mvb_rope_kv_write where bit-exact KV contents are required.
+ */
+int mvb_qk_norm_rope_kv_write(void* q, int64_t q_row_stride, void* k, int64_t k_row_stride, const void* v,
+                              int64_t v_row_stride, const void* q_weight, const void* k_weight, float eps,
+                              int unit_offset, const int64_t* positions, const float* cos_sin, int64_t max_pos,
+                              const int32_t* slot_mapping, void* k_cache, void* v_cache, int64_t num_slots,
+                              int num_tokens, int num_q_heads, int num_kv_heads, int head_dim, int k_in_place,
+                              int32_t* dev_status, void* stream);
+
+/*
  * Paged decode attention (one query token per sequence), split along the context.
  * Replaces flash_attn_with_kvcache as called at minivllm/models/layers/attention.py:90-91.
  *
@@ -188,10 +209,14 @@ int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void* k, int64_t
  *   top_k != NULL: row r keeps every logit >= its top_k[r]-th largest (top_k[r] <= 0 keeps
  *     all), adds Gumbel noise from Philox4x32-10 keyed by (seed, offset, r, column) to
  *     logit / temperature, and returns the argmax.  temperatures may be NULL (all 1).
+ *   scatter_table/scatter_index (both or neither): the token of row r is also stored at
+ *     scatter_table[scatter_index[r]], a per-request table the next decode packing reads its input
+ *     tokens from (mvb_pack_decode's prev_sampled/src_index), so the sampled ids never have to visit
+ *     the host between steps (the reference syncs on .tolist() every step, executor.py:193-195).
  */
 int mvb_sample(const void* logits, int64_t row_stride, int num_rows, int vocab, const float* temperatures,
-               const int32_t* top_k, uint64_t seed, uint64_t offset, int64_t* out, int32_t* dev_status,
-               void* stream);
+               const int32_t* top_k, uint64_t seed, uint64_t offset, int64_t* out, int64_t* scatter_table,
+               const int32_t* scatter_index, int32_t* dev_status, void* stream);
 
 #ifdef __cplusplus
 }

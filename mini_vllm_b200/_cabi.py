@@ -19,6 +19,8 @@ SIGNATURES = {
     "mvb_pack_decode": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, vp, vp, vp, vp, vp, vp, vp]),
     "mvb_rope_kv_write": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, i64, vp, vp, vp, i64, i32, i32, i32, i32, i32,
                                 vp, vp]),
+    "mvb_qk_norm_rope_kv_write": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, f32, i32, vp, vp, i64, vp, vp, vp, i64,
+                                        i32, i32, i32, i32, i32, vp, vp]),
     "mvb_decode_workspace_bytes": (sz, [i32, i32, i32]),
     "mvb_decode_plan": (i32, [vp, i32, i32, i32, i32, i32, vp, sz, vp]),
     "mvb_decode_attn": (i32, [vp, i64, vp, vp, i64, i32, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, vp, i64,
@@ -27,7 +29,7 @@ SIGNATURES = {
                                      i64, vp, vp]),
     "mvb_prefill_attn": (i32, [vp, i64, vp, i64, vp, i64, i64, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, f32,
                                i32, vp, i64, vp, vp]),
-    "mvb_sample": (i32, [vp, i64, i32, i32, vp, vp, u64, u64, vp, vp, vp]),
+    "mvb_sample": (i32, [vp, i64, i32, i32, vp, vp, u64, u64, vp, vp, vp, vp, vp]),
 }
 
 _lib = None

@@ -99,6 +99,8 @@ struct SampleParams {
   const int32_t* top_k;
   uint64_t seed, offset;
   int64_t* out;
+  int64_t* scatter_table;        // optional: table[scatter_index[row]] = token as well
+  const int32_t* scatter_index;
 };
 
 __global__ void __launch_bounds__(kSampleThreads) sample_greedy_kernel(const SampleParams p) {
@@ -114,7 +116,10 @@ __global__ void __launch_bounds__(kSampleThreads) sample_greedy_kernel(const Sam
     if (better(x, c, b.val, b.idx)) { b.val = x; b.idx = c; }
   });
   b = block_argmax(b);
-  if (threadIdx.x == 0) p.out[r] = b.idx;
+  if (threadIdx.x == 0) {
+    p.out[r] = b.idx;
+    if (p.scatter_table != nullptr) p.scatter_table[p.scatter_index[r]] = b.idx;
+  }
 }
 
 __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(const SampleParams p) {
@@ -183,19 +188,25 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
     if (better(score, c, b.val, b.idx)) { b.val = score; b.idx = c; }
   });
   b = block_argmax(b);
-  if (threadIdx.x == 0) p.out[r] = b.idx;
+  if (threadIdx.x == 0) {
+    p.out[r] = b.idx;
+    if (p.scatter_table != nullptr) p.scatter_table[p.scatter_index[r]] = b.idx;
+  }
 }
 
 }  // namespace mvb
 
 extern "C" int mvb_sample(const void* logits, int64_t row_stride, int num_rows, int vocab,
                           const float* temperatures, const int32_t* top_k, uint64_t seed, uint64_t offset,
-                          int64_t* out, int32_t* dev_status, void* stream) {
+                          int64_t* out, int64_t* scatter_table, const int32_t* scatter_index, int32_t* dev_status,
+                          void* stream) {
   using namespace mvb;
   (void)dev_status;
   if (!logits || !out || num_rows < 0 || vocab <= 0 || row_stride < vocab) return kInvalidArgument;
+  if ((scatter_table == nullptr) != (scatter_index == nullptr)) return kInvalidArgument;
   if (num_rows == 0) return kOk;
-  SampleParams p{static_cast<const uint16_t*>(logits), row_stride, vocab, temperatures, top_k, seed, offset, out};
+  SampleParams p{static_cast<const uint16_t*>(logits), row_stride, vocab, temperatures, top_k, seed, offset, out,
+                 scatter_table, scatter_index};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (top_k == nullptr) sample_greedy_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);
   else sample_topk_gumbel_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);

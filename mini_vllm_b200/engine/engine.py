@@ -5,6 +5,11 @@ random-init shape configs (no tokenizer on disk) ``prompt``/``completion`` are l
 """
 from __future__ import annotations
 
+from collections import deque
+
+import numpy as np
+import torch
+
 from ..config.config import Config
 from ..config.sampling import SamplingParams
 from ..executor.executor import Executor
@@ -43,11 +48,71 @@ class Engine:
     def finished(self) -> bool:
         return self.scheduler.finished
 
+    PLACEHOLDER = -1      # stands in Request.tokens for a sampled id that has not reached the host yet
+    RUN_AHEAD = 2         # steps the host may be ahead of the device results
+
+    def _schedule_is_token_independent(self, sampling_params) -> bool:
+        """True when no scheduling decision depends on a sampled token's value: every request stops on
+        its token budget alone and no block is published to the prefix cache."""
+        no_eos = all(sp.ignore_eos for sp in sampling_params) or not self.config.eos_token_ids
+        return no_eos and not self.config.enable_prefix_cache
+
+    def _generate_pipelined(self, reqs: list[Request]) -> None:
+        """The step loop without the per-step device-to-host sync (the reference blocks on ``.tolist()``
+        every step, executor.py:193-195).  Sampled ids stay on the device, where the next decode packing
+        picks them up; they reach ``Request.tokens`` a few steps late through a pinned buffer."""
+        ex, sch = self.executor, self.scheduler
+        slot_of = {r.id: i for i, r in enumerate(reqs)}
+        ex.ensure_token_table(len(reqs))
+        unresolved = dict.fromkeys(slot_of, 0)
+        pending: deque = deque()
+
+        def resolve(item) -> None:
+            batch_reqs, positions, host, event = item
+            event.synchronize()
+            for r, pos, tok in zip(batch_reqs, positions, host.tolist()):
+                r.tokens[pos] = tok
+                unresolved[r.id] -= 1
+
+        self._job_start = torch.cuda.Event(enable_timing=True)
+        self._job_start.record()
+        while not self.finished:
+            batch = sch.schedule()
+            if batch is None:
+                raise RuntimeError("nothing can be scheduled: a request needs more KV blocks than the pool holds")
+            if batch.type == Batch.PREFILL and any(unresolved[r.id] for r in batch.requests):
+                while pending:                      # a preempted request is re-prefilled from its real tokens
+                    resolve(pending.popleft())
+            slots = np.fromiter((slot_of[r.id] for r in batch.requests), np.int32, len(batch.requests))
+            host, event = ex.launch(batch, slots)
+            positions = [len(r.tokens) for r in batch.requests]
+            for r in batch.requests:
+                unresolved[r.id] += 1
+            sch.update(batch, [self.PLACEHOLDER] * len(batch.requests))
+            self.metrics.update(batch)
+            pending.append((list(batch.requests), positions, host, event))
+            while len(pending) > self.RUN_AHEAD:
+                resolve(pending.popleft())
+        self._job_end = torch.cuda.Event(enable_timing=True)
+        self._job_end.record()
+        while pending:
+            resolve(pending.popleft())
+
+    @property
+    def last_job_device_ms(self) -> float:
+        """Device time between the first and the last kernel of the last pipelined ``generate``."""
+        self._job_end.synchronize()
+        return self._job_start.elapsed_time(self._job_end)
+
     def generate(self, prompts: list[list[int]], sampling_params, use_tqdm: bool = True) -> list[dict]:
         if not isinstance(sampling_params, list):
             sampling_params = [sampling_params] * len(prompts)
-        for prompt, sp in zip(prompts, sampling_params):
-            self.submit(prompt, sp)
+        reqs = [self.submit(prompt, sp) for prompt, sp in zip(prompts, sampling_params)]
+        if not use_tqdm and self._schedule_is_token_independent(sampling_params):
+            self._generate_pipelined(reqs)
+            dec = self.tokenizer.decode if self.tokenizer is not None else (lambda toks: None)
+            return [{"prompt": dec(r.prompt_tokens), "completion": dec(r.completion_tokens),
+                     "tokens": r.completion_tokens} for r in sorted(reqs, key=lambda r: r.id)]
         pbar = None
         if use_tqdm:
             from tqdm.auto import tqdm

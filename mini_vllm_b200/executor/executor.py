@@ -49,6 +49,12 @@ class _Staging:
 
 
 class Executor:
+    RING = 4          # staging / result buffers in flight; the pipelined engine runs at most RING - 2 steps ahead
+
+    @property
+    def _stage(self) -> _Staging:
+        return self._stages[self._step % self.RING]
+
     def __init__(self, config):
         self.config = config
         self.device = torch.device("cuda", torch.cuda.current_device())
@@ -56,7 +62,12 @@ class Executor:
         self.model = load_model(config, self.device)
         self.sampler = Sampler(seed=config.seed)
         self.status = ops.new_status(self.device)
-        self._stage = _Staging(self.device)
+        # a ring of staging buffers: with the pipelined engine the host prepares step k+1 while the
+        # upload of step k may not have run yet
+        self._stages = [_Staging(self.device) for _ in range(self.RING)]
+        self._step = 0
+        self.token_table = torch.zeros(0, dtype=torch.int64, device=self.device)   # last token per request slot
+        self._out_ring = torch.zeros(self.RING, max(config.max_num_batched_seqs, 1), dtype=torch.int64).pin_memory()
         self.h2d_bytes = 0                   # bytes uploaded by the packing path (for the bench's e2e line)
         self.d2h_bytes = 0
         self.graph_runner = None
@@ -180,6 +191,72 @@ class Executor:
         self.d2h_bytes += tokens.numel() * 8
         return tokens.tolist()
 
+    # ---- pipelined step: nothing comes back to the host ---------------------------------------------
+    def ensure_token_table(self, num_slots: int) -> None:
+        if self.token_table.numel() < num_slots:
+            grown = torch.zeros(max(num_slots, 2 * self.token_table.numel()), dtype=torch.int64, device=self.device)
+            grown[:self.token_table.numel()] = self.token_table
+            self.token_table = grown
+
+    @torch.inference_mode()
+    def launch(self, batch: Batch, slots: np.ndarray):
+        """Enqueue one step.  The sampled tokens go to ``token_table[slots]`` on the device (the next
+        decode packing reads its input ids from there) and, asynchronously, to a pinned host buffer.
+
+        Returns ``(pinned int64 view, event)``: the view holds the tokens once the event has completed.
+        Decode input tokens are NOT taken from ``Request.tokens`` (they may still be placeholders).
+        """
+        reqs, b = batch.requests, len(batch.requests)
+        self._step += 1
+        if batch.type == Batch.PREFILL:
+            seq_len, nblk, blk_off, blocks = self._per_seq(reqs)
+            cached = np.fromiter((r.num_cached_tokens for r in reqs), np.int32, b)
+            q_len = seq_len - cached
+            t = int(q_len.sum())
+            new_tokens = np.fromiter(
+                itertools.chain.from_iterable(r.tokens[r.num_cached_tokens:] if r.num_cached_tokens else r.tokens
+                                              for r in reqs), np.int32, t)
+            meta = self._stage.upload([seq_len, cached, blk_off, blocks, new_tokens, slots])
+            slots_dev = meta[meta.numel() - b:]
+            width = max(int(nblk.max()), 1)
+            out = ops.pack_prefill(meta, b, t, int(blk_off[-1]), width, self.block_size, bool(cached.any()), self.status)
+            ctx = Context(prefill=True, positions=out["positions"], cu_seqlens_q=out["cu_seqlens_q"],
+                          cu_seqlens_k=out["cu_seqlens_k"], slot_mapping=out["slot_mapping"],
+                          max_seqlen_q=int(q_len.max()), max_seqlen_k=int(seq_len.max()),
+                          block_table=out["block_table"], status=self.status)
+            input_ids = out["input_ids"]
+        else:
+            seq_len, nblk, blk_off, blocks = self._per_seq(reqs)
+            meta = self._stage.upload([seq_len, blk_off, blocks, np.zeros(b, np.int32), slots])
+            slots_dev = meta[meta.numel() - b:]
+            nblocks, width = int(blk_off[-1]), int(nblk.max())
+            gr = self.graph_runner
+            if gr is not None and gr.max_batch_size >= b:
+                ops.pack_decode(meta, b, nblocks, width, self.block_size, gr.input_ids, gr.positions, gr.slot_mapping,
+                                gr.cache_seqlens, gr.block_table, padded_seqs=gr.padded_size(b),
+                                prev_sampled=self.token_table, status=self.status)
+                input_ids, ctx = gr.input_ids[:b], gr.static_context(b)
+            else:
+                dev = self.device
+                input_ids, pos = torch.empty(b, dtype=torch.int64, device=dev), torch.empty(b, dtype=torch.int64, device=dev)
+                slot, lens = torch.empty(b, dtype=torch.int32, device=dev), torch.empty(b, dtype=torch.int32, device=dev)
+                table = torch.empty(b, width, dtype=torch.int32, device=dev)
+                ops.pack_decode(meta, b, nblocks, width, self.block_size, input_ids, pos, slot, lens, table,
+                                prev_sampled=self.token_table, status=self.status)
+                ctx = Context(prefill=False, positions=pos, slot_mapping=slot, cache_seqlens=lens, block_table=table,
+                              status=self.status)
+        self.h2d_bytes += meta.numel() * 4
+        logits = self.forward(ctx, input_ids)
+        temperatures, top_k, top_p = self._build_sample_input(reqs)
+        tokens = self.sampler(logits, temperatures, top_p=top_p, top_k=top_k, scatter_table=self.token_table,
+                              scatter_index=slots_dev)
+        host = self._out_ring[self._step % self.RING, :b]
+        host.copy_(tokens, non_blocking=True)
+        self.d2h_bytes += b * 8
+        event = torch.cuda.Event()
+        event.record()
+        return host, event
+
     # ---- forward ---------------------------------------------------------------------------------
     def prefill(self, ctx: Context, input_ids: torch.Tensor) -> torch.Tensor:
         return self.model(ctx, input_ids, ctx.positions)
@@ -195,6 +272,7 @@ class Executor:
 
     @torch.inference_mode()
     def execute(self, batch: Batch) -> list[int]:
+        self._step += 1
         if batch.type == Batch.PREFILL:
             input_ids, ctx = self._build_prefill_input(batch.requests)
         else:

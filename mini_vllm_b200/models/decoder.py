@@ -11,8 +11,9 @@ embedding stay PyTorch/cuBLAS, wired the way the reference wires them:
   scaled by ``sqrt(hidden)`` (``:175-184``), a global and a local RoPE table and a sliding
   window on every layer whose index ``i`` has ``(i + 1) % 6 != 0`` (``:196-211``).
 
-q/k/v come out of ONE packed projection (row stride != heads * head_dim), are normalised, and go
-straight into ``FlashAttention.forward_fused`` which rotates and writes the KV cache in one kernel.
+q/k/v come out of ONE packed projection (row stride != heads * head_dim) and go straight into
+``FlashAttention.forward_fused_norm``: per-head RMSNorm, RoPE and the KV-cache write are one kernel that
+works in place on the projection output.
 """
 from __future__ import annotations
 
@@ -56,10 +57,10 @@ class Attention(nn.Module):
 
     def forward(self, ctx: Context, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         q, k, v = self.qkv_proj(x).split([self.q_dim, self.kv_dim, self.kv_dim], dim=-1)
-        q = self.q_norm(q.view(-1, self.hq, self.d))
-        k = self.k_norm(k.view(-1, self.hkv, self.d))
-        v = v.view(-1, self.hkv, self.d)
-        o = self.attn.forward_fused(ctx, q, k, v, positions, self.rotary.cos_sin_cache)
+        q, k, v = q.view(-1, self.hq, self.d), k.view(-1, self.hkv, self.d), v.view(-1, self.hkv, self.d)
+        # per-head norms, RoPE and the KV write run as one kernel on the packed projection output
+        o = self.attn.forward_fused_norm(ctx, q, k, v, positions, self.rotary.cos_sin_cache, self.q_norm.weight,
+                                         self.k_norm.weight, self.q_norm.eps, self.q_norm.unit_offset)
         return self.o_proj(o.reshape(-1, self.q_dim))
 
 

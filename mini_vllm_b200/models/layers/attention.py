@@ -70,6 +70,18 @@ class FlashAttention(nn.Module):
                           k_in_place=ctx.prefill and ctx.block_table is None, status=ctx.status)
         return self._attend(ctx, q, k, v)
 
+    def forward_fused_norm(self, ctx: Context, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                           positions: torch.Tensor, cos_sin_cache: torch.Tensor, q_weight: torch.Tensor,
+                           k_weight: torch.Tensor, eps: float, unit_offset: bool) -> torch.Tensor:
+        """q, k straight from the projection (views of the packed qkv output): per-head RMSNorm, RoPE
+        and the cache write in one kernel (q and k updated in place), then attention."""
+        has_cache = self._has_cache()
+        ops.qk_norm_rope_kv_write(q, k, v, q_weight, k_weight, eps, unit_offset, positions, cos_sin_cache,
+                                  ctx.slot_mapping if has_cache else None, self.k_cache if has_cache else None,
+                                  self.v_cache if has_cache else None,
+                                  k_in_place=ctx.prefill and ctx.block_table is None, status=ctx.status)
+        return self._attend(ctx, q, k, v)
+
     def _attend(self, ctx: Context, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
         if ctx.prefill:
             if ctx.block_table is not None:        # prefix cache in play: keys come from the pool

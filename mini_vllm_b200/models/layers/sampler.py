@@ -24,13 +24,16 @@ class Sampler(nn.Module):
         self.offset = 0            # advanced once per random draw so steps use fresh noise
 
     def forward(self, logits: torch.Tensor, temperatures: Optional[torch.Tensor] = None,
-                top_p: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None) -> torch.Tensor:
+                top_p: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None,
+                scatter_table: Optional[torch.Tensor] = None, scatter_index: Optional[torch.Tensor] = None
+                ) -> torch.Tensor:
         if logits.dtype != torch.bfloat16:
             logits = logits.to(torch.bfloat16)
         if top_p is not None and bool((top_p < 1.0).any()):
             raise NotImplementedError("top-p sampling is not implemented; use top_k")
         if top_k is None:
-            return ops.sample(logits, temperatures)
-        out = ops.sample(logits, temperatures, top_k, self.seed, self.offset)
+            return ops.sample(logits, temperatures, scatter_table=scatter_table, scatter_index=scatter_index)
+        out = ops.sample(logits, temperatures, top_k, self.seed, self.offset, scatter_table=scatter_table,
+                         scatter_index=scatter_index)
         self.offset += 1
         return out

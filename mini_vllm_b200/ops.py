@@ -151,6 +151,34 @@ def rope_kv_write(q: torch.Tensor | None, k: torch.Tensor, v: torch.Tensor, posi
     LaunchCounter.add(1)
 
 
+def qk_norm_rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_weight: torch.Tensor,
+                          k_weight: torch.Tensor, eps: float, unit_offset: bool, positions: torch.Tensor,
+                          cos_sin: torch.Tensor, slot_mapping: torch.Tensor | None, k_cache: torch.Tensor | None,
+                          v_cache: torch.Tensor | None, k_in_place: bool = True,
+                          status: torch.Tensor | None = None) -> None:
+    """Per-head RMSNorm of q and k, RoPE and the cache write in one kernel; q (and k) updated in place."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _need(t, torch.bfloat16, n); _heads_contiguous(t, n)
+    _need(q_weight, torch.bfloat16, "q_weight"); _need(k_weight, torch.bfloat16, "k_weight")
+    _need(cos_sin, torch.float32, "cos_sin"); _need(positions, torch.int64, "positions")
+    T, hkv, d = k.shape
+    hq = q.shape[1]
+    assert q.shape[0] == T and q.shape[2] == d and cos_sin.is_contiguous() and cos_sin.shape[1] == d
+    assert q_weight.numel() == d and k_weight.numel() == d and q_weight.is_contiguous() and k_weight.is_contiguous()
+    num_slots = 0
+    if slot_mapping is not None:
+        _need(slot_mapping, torch.int32, "slot_mapping")
+        assert slot_mapping.numel() == T and k_cache.is_contiguous() and v_cache.is_contiguous()
+        num_slots = k_cache.shape[0] * k_cache.shape[1]
+    rc = _cabi.load().mvb_qk_norm_rope_kv_write(
+        _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(q_weight), _ptr(k_weight), float(eps),
+        1 if unit_offset else 0, _ptr(positions), _ptr(cos_sin), cos_sin.shape[0], _ptr(slot_mapping),
+        _ptr(k_cache) if slot_mapping is not None else None, _ptr(v_cache) if slot_mapping is not None else None,
+        num_slots, T, hq, hkv, d, 1 if k_in_place else 0, _ptr(status), _stream())
+    _cabi.check(rc, "mvb_qk_norm_rope_kv_write")
+    LaunchCounter.add(1)
+
+
 def decode_workspace(max_seqs: int, num_q_heads: int, head_dim: int, device) -> torch.Tensor:
     n = _cabi.load().mvb_decode_workspace_bytes(max_seqs, num_q_heads, head_dim)
     if n == 0:
@@ -243,8 +271,12 @@ def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q
 
 
 def sample(logits: torch.Tensor, temperatures: torch.Tensor | None = None, top_k: torch.Tensor | None = None,
-           seed: int = 0, offset: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
-    """logits bf16 [B,V] -> int64 [B].  top_k None: greedy; else temperature/top-k/Gumbel-max."""
+           seed: int = 0, offset: int = 0, out: torch.Tensor | None = None,
+           scatter_table: torch.Tensor | None = None, scatter_index: torch.Tensor | None = None) -> torch.Tensor:
+    """logits bf16 [B,V] -> int64 [B].  top_k None: greedy; else temperature/top-k/Gumbel-max.
+
+    With ``scatter_table`` (int64) and ``scatter_index`` (int32 [B]) the tokens are also written to
+    ``scatter_table[scatter_index]`` on the device."""
     _need(logits, torch.bfloat16, "logits")
     assert logits.dim() == 2 and logits.stride(1) == 1
     B, V = logits.shape
@@ -254,8 +286,12 @@ def sample(logits: torch.Tensor, temperatures: torch.Tensor | None = None, top_k
         _need(top_k, torch.int32, "top_k")
     if out is None:
         out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    if scatter_table is not None:
+        _need(scatter_table, torch.int64, "scatter_table"); _need(scatter_index, torch.int32, "scatter_index")
+        assert scatter_index.numel() >= B
     rc = _cabi.load().mvb_sample(_ptr(logits), logits.stride(0), B, V, _ptr(temperatures), _ptr(top_k),
-                                 seed & (2**64 - 1), offset & (2**64 - 1), _ptr(out), None, _stream())
+                                 seed & (2**64 - 1), offset & (2**64 - 1), _ptr(out), _ptr(scatter_table),
+                                 _ptr(scatter_index), None, _stream())
     _cabi.check(rc, "mvb_sample")
     LaunchCounter.add(1)
     return out

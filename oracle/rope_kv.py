@@ -43,3 +43,13 @@ def store_kvcache(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor,
     idx = slot_mapping[keep].long()
     k_cache.view(-1, h * d).index_copy_(0, idx, key.reshape(n, h * d)[keep])
     v_cache.view(-1, h * d).index_copy_(0, idx, value.reshape(n, h * d)[keep])
+
+
+def qk_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, unit_offset: bool) -> torch.Tensor:
+    """Per-head RMSNorm as the models apply it before RoPE: ``nn.RMSNorm`` (qwen3.py:64-65,89-90) or
+    Gemma's fp32 ``(1 + w)`` form (gemma3.py:12-24,97-98)."""
+    if not unit_offset:
+        return torch.nn.functional.rms_norm(x, (x.shape[-1],), weight, eps)
+    xf = x.float()
+    xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (xf * (1.0 + weight.float())).type_as(x)

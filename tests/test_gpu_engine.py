@@ -103,6 +103,23 @@ def test_prefix_cache_and_preemption_match_oracle(cuda):
     check_tokens(engine, "qwen3", prompts, params, cfg, got)
 
 
+def test_pipelined_loop_with_preemption_matches_oracle(cuda):
+    """A pool too small for everybody (requests get preempted and re-prefilled) under the pipelined step loop,
+    where sampled ids reach the host late: still the oracle's tokens."""
+    g = generator(7)
+    prompts = [torch.randint(0, 2048, (int(n),), generator=g).tolist() for n in randint(g, 30, 500, 10)]
+    params = [SamplingParams(max_tokens=150, ignore_eos=True) for _ in prompts]
+    cfg = Config(hf_config=small_qwen3(), kv_cache_num_blocks=9, max_num_batched_seqs=6,
+                 max_num_batched_tokens=4096, gpu_memory_utilization=0.3, seed=5)
+    engine = Engine(cfg)
+    assert engine._schedule_is_token_independent(params)
+    out = engine.generate(prompts, copy.deepcopy(params), use_tqdm=False)
+    engine.executor.check_device_status()
+    got = [o["tokens"] for o in out]
+    assert all(len(t) == 150 and min(t) >= 0 for t in got)
+    check_tokens(engine, "qwen3", prompts, params, cfg, got)
+
+
 def test_sampling_params_paths(cuda):
     """Temperature alone stays greedy (reference behaviour); top-k draws are seeded and reproducible."""
     g = generator(8)

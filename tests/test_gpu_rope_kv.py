@@ -96,3 +96,36 @@ def test_out_of_range_slot_and_position_are_reported(cuda):
     ops.rope_kv_write(q, k, v, torch.tensor([0, 1, 2, 77], device=cuda), table, None, None, None, status=status)
     torch.cuda.synchronize()
     assert status[0].item() == 3 and status[1].item() == 3
+
+
+@pytest.mark.parametrize("hq,hkv,d,unit_offset", [(16, 8, 128, False), (4, 1, 256, True), (8, 2, 128, True)])
+def test_fused_qk_norm_rope_write_matches_unfused_sequence(cuda, hq, hkv, d, unit_offset):
+    """norm -> bf16 -> RoPE -> cache, fused: equal to the oracle up to the summation order of the squares."""
+    g = generator(21)
+    T, nblk, bs, max_pos, eps = 257, 4, 256, 4096, 1e-6
+    table = rope_kv.cos_sin_table(d, max_pos, 1e6)
+    qkv = randn_bf16(g, T, (hq + 2 * hkv) * d) * 3
+    qw, kw = randn_bf16(g, d) * 0.5 + (0 if unit_offset else 1), randn_bf16(g, d) * 0.5 + (0 if unit_offset else 1)
+    pos = torch.randint(0, max_pos, (T,), generator=g)
+    slots = torch.randperm(nblk * bs, generator=g)[:T].to(torch.int32)
+    slots[::5] = -1
+    q, k, v = (t.view(T, -1, d) for t in qkv.split([hq * d, hkv * d, hkv * d], dim=-1))
+    qn, kn = rope_kv.qk_norm(q, qw, eps, unit_offset), rope_kv.qk_norm(k, kw, eps, unit_offset)
+    q_ref, k_ref = rope_kv.apply_rope(pos, qn, kn, table)
+    kc_ref, vc_ref = torch.zeros(nblk, bs, hkv, d, dtype=torch.bfloat16), torch.zeros(nblk, bs, hkv, d, dtype=torch.bfloat16)
+    rope_kv.store_kvcache(k_ref, v, kc_ref, vc_ref, slots)
+
+    qkv_d = qkv.to(cuda)
+    qd, kd, vd = (t.view(T, -1, d) for t in qkv_d.split([hq * d, hkv * d, hkv * d], dim=-1))
+    kc, vc = torch.zeros_like(kc_ref, device=cuda), torch.zeros_like(vc_ref, device=cuda)
+    status = ops.new_status(cuda)
+    ops.qk_norm_rope_kv_write(qd, kd, vd, qw.to(cuda), kw.to(cuda), eps, unit_offset, pos.to(cuda), table.to(cuda),
+                              slots.to(cuda), kc, vc, k_in_place=True, status=status)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    assert torch.equal(bits(vc), bits(vc_ref)) and torch.equal(bits(vd), bits(v))          # V is a pure copy
+    for got, want, name in ((qd, q_ref, "q"), (kd, k_ref, "k"), (kc, kc_ref, "k_cache")):
+        got, want = got.float().cpu(), want.float()
+        same = (got == want).float().mean().item()
+        rel = ((got - want).abs() / want.abs().clamp_min(1.0)).max().item()      # one bf16 ulp of O(1) values
+        assert same >= 0.995 and rel <= 2 ** -6, f"{name}: {same:.5f} equal, max rel diff {rel:.4g}"
