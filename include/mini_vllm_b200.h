@@ -218,6 +218,27 @@ int mvb_sample(const void* logits, int64_t row_stride, int num_rows, int vocab, 
                const int32_t* top_k, uint64_t seed, uint64_t offset, int64_t* out, int64_t* scatter_table,
                const int32_t* scatter_index, int32_t* dev_status, void* stream);
 
+/*
+ * Decoder-layer glue around the attention path.  A decode step of a small model is bound by the number
+ * of kernels it launches, so the elementwise chains the models run between their GEMMs are fused.
+ *
+ * mvb_act_mul: out[t, i] = act(gate_up[t, i]) * gate_up[t, intermediate + i] on a packed
+ *   [rows, 2 * intermediate] projection; act = SiLU (minivllm/models/models/qwen3.py:117-121) or
+ *   tanh-GELU (gelu_tanh != 0, minivllm/models/models/gemma3.py:122-128).  The activation is rounded
+ *   to bf16 before the product, as the unfused sequence rounds it.
+ * mvb_add_rmsnorm: the residual update and the next RMSNorm of a decoder layer in one pass over a row:
+ *     y' = y                       (y_weight == NULL; qwen3.py:146-155)
+ *     y' = rmsnorm(y, y_weight)    (Gemma's post-attention / post-feedforward norm, gemma3.py:157-170)
+ *     x  = bf16(x + y')            (in place, x is [rows, hidden] contiguous)
+ *     out = rmsnorm(x, weight)     (the following input / post-attention / pre-feedforward / final norm)
+ *   rmsnorm(v, w) = v * rsqrt(mean(v^2) + eps) * w, or * (1 + w) when unit_offset != 0, in fp32.
+ *   hidden must be a multiple of 8 and at most 8192.
+ */
+int mvb_act_mul(const void* gate_up, int64_t in_row_stride, void* out, int64_t out_row_stride, int rows,
+                int intermediate, int gelu_tanh, void* stream);
+int mvb_add_rmsnorm(void* x, const void* y, int64_t y_row_stride, const void* y_weight, const void* weight,
+                    void* out, int rows, int hidden, float eps, int unit_offset, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,175 @@
+// Glue kernels of the decoder layer around the attention path.  A decode step of a small model is
+// bound by the NUMBER of kernels (a few microseconds each, whatever their size), so the elementwise
+// chains between the GEMMs are fused: activation * up-projection, and residual add + RMSNorm
+// (optionally with Gemma's extra norm on the branch output).  Each intermediate is rounded to bf16
+// where the unfused PyTorch sequence would round it, so results match that sequence to an ulp.
+#include "common.cuh"
+#include "mini_vllm_b200.h"
+
+namespace mvb {
+
+__device__ __forceinline__ float act_silu(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float act_gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i]
+__global__ void __launch_bounds__(256) act_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, int64_t in_stride,
+                                                     __nv_bfloat16* __restrict__ out, int64_t out_stride, int rows,
+                                                     int inter, int gelu) {
+  const int chunks = inter / 8;
+  const int64_t total = static_cast<int64_t>(rows) * chunks;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < total;
+       g += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(g / chunks), c = static_cast<int>(g - static_cast<int64_t>(t) * chunks);
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate_up + t * in_stride + c * 8);
+    const uint4 uv = *reinterpret_cast<const uint4*>(gate_up + t * in_stride + inter + c * 8);
+    const uint32_t* ga = reinterpret_cast<const uint32_t*>(&gv);
+    const uint32_t* ua = reinterpret_cast<const uint32_t*>(&uv);
+    uint4 ov;
+    uint32_t* oa = reinterpret_cast<uint32_t*>(&ov);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float g0 = bf16_lo(ga[i]), g1 = bf16_hi(ga[i]);
+      const float a0 = round_bf16(gelu ? act_gelu_tanh(g0) : act_silu(g0));
+      const float a1 = round_bf16(gelu ? act_gelu_tanh(g1) : act_silu(g1));
+      oa[i] = pack_bf16(a0 * bf16_lo(ua[i]), a1 * bf16_hi(ua[i]));
+    }
+    *reinterpret_cast<uint4*>(out + t * out_stride + c * 8) = ov;
+  }
+}
+
+// One CTA per row.  y' = y (or rmsnorm(y, y_weight) rounded to bf16);  x = bf16(x + y');
+// out = rmsnorm(x, weight).  Norms are fp32: v * rsqrt(mean(v^2) + eps) * w  (or * (1 + w)).
+constexpr int kNormThreads = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();                                           // scratch may still be read from a previous call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int w = 0; w < kNormThreads / 32; ++w) s += scratch[w];
+  return s;
+}
+
+template <int VPT>                                           // 8-element vectors per thread (hidden <= 256 * 8 * VPT)
+__global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16* __restrict__ x,
+                                                                  const __nv_bfloat16* __restrict__ y, int64_t y_stride,
+                                                                  const __nv_bfloat16* __restrict__ y_weight,
+                                                                  const __nv_bfloat16* __restrict__ weight,
+                                                                  __nv_bfloat16* __restrict__ out, int hidden,
+                                                                  float eps, int unit_offset) {
+  __shared__ float scratch[kNormThreads / 32];
+  const int row = blockIdx.x;
+  const int nvec = hidden / 8;
+  const float one = unit_offset ? 1.f : 0.f;
+  float xv[VPT][8];
+  // ---- branch output, optionally normalised first (Gemma's post-attention / post-feedforward norm)
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * kNormThreads;
+    if (v < nvec) {
+      const uint4 yv = *reinterpret_cast<const uint4*>(y + row * y_stride + v * 8);
+      const uint32_t* ya = reinterpret_cast<const uint32_t*>(&yv);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { xv[k][2 * i] = bf16_lo(ya[i]); xv[k][2 * i + 1] = bf16_hi(ya[i]); }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += xv[k][i] * xv[k][i];
+    }
+  }
+  if (y_weight != nullptr) {
+    const float rstd = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = threadIdx.x + k * kNormThreads;
+      if (v < nvec) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(y_weight + v * 8);
+        const uint32_t* wa = reinterpret_cast<const uint32_t*>(&wv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          xv[k][2 * i] = round_bf16(xv[k][2 * i] * rstd * (one + bf16_lo(wa[i])));
+          xv[k][2 * i + 1] = round_bf16(xv[k][2 * i + 1] * rstd * (one + bf16_hi(wa[i])));
+        }
+      }
+    }
+  }
+  // ---- residual add (rounded to bf16, written back) and the norm of the new residual stream
+  ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * kNormThreads;
+    if (v < nvec) {
+      uint4 rv = *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(row) * hidden + v * 8);
+      uint32_t* ra = reinterpret_cast<uint32_t*>(&rv);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ra[i] = pack_bf16(bf16_lo(ra[i]) + xv[k][2 * i], bf16_hi(ra[i]) + xv[k][2 * i + 1]);
+        xv[k][2 * i] = bf16_lo(ra[i]); xv[k][2 * i + 1] = bf16_hi(ra[i]);
+      }
+      *reinterpret_cast<uint4*>(x + static_cast<int64_t>(row) * hidden + v * 8) = rv;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += xv[k][i] * xv[k][i];
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * kNormThreads;
+    if (v < nvec) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(weight + v * 8);
+      const uint32_t* wa = reinterpret_cast<const uint32_t*>(&wv);
+      uint4 ov;
+      uint32_t* oa = reinterpret_cast<uint32_t*>(&ov);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        oa[i] = pack_bf16(xv[k][2 * i] * rstd * (one + bf16_lo(wa[i])), xv[k][2 * i + 1] * rstd * (one + bf16_hi(wa[i])));
+      *reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * hidden + v * 8) = ov;
+    }
+  }
+}
+
+static bool a16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace mvb
+
+extern "C" int mvb_act_mul(const void* gate_up, int64_t in_row_stride, void* out, int64_t out_row_stride, int rows,
+                           int intermediate, int gelu_tanh, void* stream) {
+  using namespace mvb;
+  if (!gate_up || !out || rows < 0 || intermediate <= 0) return kInvalidArgument;
+  if (intermediate % 8 || in_row_stride % 8 || out_row_stride % 8 || !a16(gate_up) || !a16(out)) return kMisaligned;
+  if (rows == 0) return kOk;
+  const int64_t total = static_cast<int64_t>(rows) * (intermediate / 8);
+  int blocks = static_cast<int>((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  act_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), in_row_stride, static_cast<__nv_bfloat16*>(out), out_row_stride, rows,
+      intermediate, gelu_tanh);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+extern "C" int mvb_add_rmsnorm(void* x, const void* y, int64_t y_row_stride, const void* y_weight, const void* weight,
+                               void* out, int rows, int hidden, float eps, int unit_offset, void* stream) {
+  using namespace mvb;
+  if (!x || !y || !weight || !out || rows < 0 || hidden <= 0) return kInvalidArgument;
+  if (hidden % 8 || y_row_stride % 8 || !a16(x) || !a16(y) || !a16(weight) || !a16(out) || !a16(y_weight)) return kMisaligned;
+  if (hidden > kNormThreads * 8 * 4) return kUnsupportedShape;
+  if (rows == 0) return kOk;
+  auto* xp = static_cast<__nv_bfloat16*>(x);
+  auto* yp = static_cast<const __nv_bfloat16*>(y);
+  auto* ywp = static_cast<const __nv_bfloat16*>(y_weight);
+  auto* wp = static_cast<const __nv_bfloat16*>(weight);
+  auto* op = static_cast<__nv_bfloat16*>(out);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int vpt = (hidden / 8 + kNormThreads - 1) / kNormThreads;
+  if (vpt <= 1) add_rmsnorm_kernel<1><<<rows, kNormThreads, 0, st>>>(xp, yp, y_row_stride, ywp, wp, op, hidden, eps, unit_offset);
+  else if (vpt == 2) add_rmsnorm_kernel<2><<<rows, kNormThreads, 0, st>>>(xp, yp, y_row_stride, ywp, wp, op, hidden, eps, unit_offset);
+  else add_rmsnorm_kernel<4><<<rows, kNormThreads, 0, st>>>(xp, yp, y_row_stride, ywp, wp, op, hidden, eps, unit_offset);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}

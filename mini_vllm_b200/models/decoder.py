@@ -23,6 +23,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from .. import ops
 from ..executor.context import Context
 from .layers.attention import FlashAttention
 from .layers.rotary import RotaryEmbedding
@@ -72,9 +73,7 @@ class GatedMLP(nn.Module):
         self.down_proj = nn.Linear(self.inter, cfg.hidden_size, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        gate, up = self.gate_up_proj(x).split([self.inter, self.inter], dim=-1)
-        act = F.gelu(gate, approximate="tanh") if self.gemma else F.silu(gate)
-        return self.down_proj(act * up)
+        return self.down_proj(ops.act_mul(self.gate_up_proj(x), self.inter, self.gemma))
 
 
 class DecoderLayer(nn.Module):
@@ -88,12 +87,21 @@ class DecoderLayer(nn.Module):
         if gemma:
             self.pre_feedforward_layernorm, self.post_feedforward_layernorm = norm(), norm()
 
-    def forward(self, ctx: Context, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx: Context, x: torch.Tensor, h: torch.Tensor, positions: torch.Tensor,
+                next_norm: RMSNorm) -> torch.Tensor:
+        """``x`` is the residual stream (updated in place), ``h`` its already normalised copy for this
+        layer; returns the normalised input of the next layer (``next_norm`` applied to the new ``x``).
+        Each residual add is fused with the norm that follows it (and, for Gemma, with the norm on the
+        branch output), which is the reference's dataflow (qwen3.py:146-155, gemma3.py:157-170)."""
+        a = self.self_attn(ctx, h, positions)
         if not self.gemma:
-            x = x + self.self_attn(ctx, self.input_layernorm(x), positions)
-            return x + self.mlp(self.post_attention_layernorm(x))
-        x = x + self.post_attention_layernorm(self.self_attn(ctx, self.input_layernorm(x), positions))
-        return x + self.post_feedforward_layernorm(self.mlp(self.pre_feedforward_layernorm(x)))
+            n = self.post_attention_layernorm
+            h = ops.add_rmsnorm(x, a, n.weight, n.eps, False)
+            return ops.add_rmsnorm(x, self.mlp(h), next_norm.weight, next_norm.eps, False)
+        n = self.pre_feedforward_layernorm
+        h = ops.add_rmsnorm(x, a, n.weight, n.eps, True, y_weight=self.post_attention_layernorm.weight)
+        return ops.add_rmsnorm(x, self.mlp(h), next_norm.weight, next_norm.eps, True,
+                               y_weight=self.post_feedforward_layernorm.weight)
 
 
 class DecoderLM(nn.Module):
@@ -128,9 +136,12 @@ class DecoderLM(nn.Module):
         x = self.embed_tokens(input_ids)
         if self.embed_scale is not None:
             x = x * self.embed_scale.to(x.dtype)
-        for layer in self.layers:
-            x = layer(ctx, x, positions)
-        x = self.norm(x)
+        x = x.contiguous()
+        h = self.layers[0].input_layernorm(x)
+        for i, layer in enumerate(self.layers):
+            nxt = self.layers[i + 1].input_layernorm if i + 1 < len(self.layers) else self.norm
+            h = layer(ctx, x, h, positions, nxt)
+        x = h                                                  # the final norm is already applied
         if ctx.prefill:
             x = x[ctx.cu_seqlens_q[1:] - 1].contiguous()
         return self.lm_head(x)

@@ -295,3 +295,32 @@ def sample(logits: torch.Tensor, temperatures: torch.Tensor | None = None, top_k
     _cabi.check(rc, "mvb_sample")
     LaunchCounter.add(1)
     return out
+
+
+def act_mul(gate_up: torch.Tensor, intermediate: int, gelu_tanh: bool, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``act(gate) * up`` on a packed ``[rows, 2 * intermediate]`` projection (SiLU, or tanh-GELU)."""
+    _need(gate_up, torch.bfloat16, "gate_up")
+    assert gate_up.dim() == 2 and gate_up.stride(1) == 1 and gate_up.shape[1] == 2 * intermediate
+    rows = gate_up.shape[0]
+    if out is None:
+        out = torch.empty(rows, intermediate, dtype=torch.bfloat16, device=gate_up.device)
+    rc = _cabi.load().mvb_act_mul(_ptr(gate_up), gate_up.stride(0), _ptr(out), out.stride(0), rows, intermediate,
+                                  1 if gelu_tanh else 0, _stream())
+    _cabi.check(rc, "mvb_act_mul")
+    LaunchCounter.add(1)
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, unit_offset: bool,
+                y_weight: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x += y`` (or ``x += rmsnorm(y, y_weight)``) in place, returns ``rmsnorm(x, weight)``."""
+    _need(x, torch.bfloat16, "x"); _need(y, torch.bfloat16, "y"); _need(weight, torch.bfloat16, "weight")
+    assert x.dim() == 2 and x.is_contiguous() and y.shape == x.shape and y.stride(1) == 1
+    rows, hidden = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    rc = _cabi.load().mvb_add_rmsnorm(_ptr(x), _ptr(y), y.stride(0), _ptr(y_weight), _ptr(weight), _ptr(out), rows,
+                                      hidden, float(eps), 1 if unit_offset else 0, _stream())
+    _cabi.check(rc, "mvb_add_rmsnorm")
+    LaunchCounter.add(1)
+    return out
