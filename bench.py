@@ -42,8 +42,8 @@ sys.path.insert(0, str(ROOT))
 
 from mini_vllm_b200.config import Config, SamplingParams, qwen3_shape  # noqa: E402
 from mini_vllm_b200.dispatcher import partition_by_tokens  # noqa: E402
-from mini_vllm_b200.workloads import (QWEN3_0P6B, config2_requests, config3, decode_kv_bytes,  # noqa: E402
-                                       prefill_flops)
+from mini_vllm_b200.workloads import (GEMMA3_1B, QWEN3_0P6B, config2_requests, config3, config4,  # noqa: E402
+                                       decode_kv_bytes, prefill_flops)
 
 METRIC = "ragged prefill+decode tokens/s (Qwen3-0.6B shapes, 64 requests per GPU, greedy)"
 WORKLOAD = "config2: Qwen3-0.6B random-init, 64 req/GPU, prompt U[100,1024], total<=1024, continuous batching"
@@ -236,6 +236,41 @@ def kernel_extras(dev, peaks, nl=4):
     tf = fl / ms / 1e9
     out["prefill_attn_config3"] = {"TFLOP/s": round(tf, 1), "us": round(ms * 1e3, 1), "flops": fl,
                                    "frac_of_measured_bf16": round(tf / peaks["bf16_tflops"], 4)}
+    del pools
+    # Gemma3-1B shapes (4 q heads, 1 kv head, head_dim 256), 128 sequences, contexts U[512,4096]:
+    # a global layer and a sliding-window-512 layer (window layers count only the visible keys)
+    g4, _ = config4()
+    hq, hkv, d = 4, 1, 256
+    gpools = [torch.randn(2, g4.pool_blocks, 256, hkv, d, device=dev, dtype=torch.bfloat16) for _ in range(max(nl, 2) * 2)]
+    b = len(g4.decode_ctx)
+    q = torch.randn(b, hq, d, device=dev, dtype=torch.bfloat16)
+    lens = torch.tensor(g4.decode_ctx, dtype=torch.int32, device=dev)
+    bt = table_tensor(g4.decode_blocks).to(dev)
+    o = torch.empty_like(q)
+    for name, window in (("decode_attn_config4_global", -1), ("decode_attn_config4_window512", 512)):
+        ws = ops.decode_workspace(b, hq, d, dev)
+        ops.decode_plan(lens, window, hq, hkv, d, ws)
+
+        def layer_sweep():
+            for gp in gpools:
+                ops.decode_attn(q, gp[0], gp[1], lens, bt, d ** -0.5, window, ws, out=o)
+        layer_sweep()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()                       # short kernels: time device time, not the launch rate
+        with torch.cuda.graph(graph):
+            layer_sweep()
+        graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (5 * len(gpools))
+        byts = decode_kv_bytes(GEMMA3_1B, g4.decode_ctx, window)
+        gbs = byts / ms / 1e6
+        out[name] = {"GB/s": round(gbs, 1), "us": round(ms * 1e3, 1), "bytes": byts,
+                     "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4)}
     return out
 
 
