@@ -149,7 +149,7 @@ def decode_roofline(engine, contexts, peaks):
         bt = table_tensor(blocks).to(dev)
         ws = ops.decode_workspace(b, hq, d, dev)
         out = torch.empty_like(q)
-        ops.decode_plan(seqlens, -1, hq, hkv, d, ws)
+        ops.decode_plan(seqlens, -1, hq, hkv, d, ws, block_table=bt, block_size=256)
         def all_layers():                                        # distinct layer pools: no L2 reuse between launches
             for layer in range(layers):
                 ops.decode_attn(q, ex.kv_cache[0, layer], ex.kv_cache[1, layer], seqlens, bt, d ** -0.5, -1, ws, out=out)
@@ -200,7 +200,7 @@ def kernel_extras(dev, peaks, nl=4):
     bt = table_tensor(case.decode_blocks).to(dev)
     ws = ops.decode_workspace(b, hq, d, dev)
     o = torch.empty_like(q)
-    ops.decode_plan(lens, -1, hq, hkv, d, ws)
+    ops.decode_plan(lens, -1, hq, hkv, d, ws, block_table=bt, block_size=256)
     iters = 24
     for i in range(8):
         ops.decode_attn(q, pools[i % nl][0], pools[i % nl][1], lens, bt, d ** -0.5, -1, ws, out=o)
@@ -249,7 +249,7 @@ def kernel_extras(dev, peaks, nl=4):
     o = torch.empty_like(q)
     for name, window in (("decode_attn_config4_global", -1), ("decode_attn_config4_window512", 512)):
         ws = ops.decode_workspace(b, hq, d, dev)
-        ops.decode_plan(lens, window, hq, hkv, d, ws)
+        ops.decode_plan(lens, window, hq, hkv, d, ws, block_table=bt, block_size=256)
 
         def layer_sweep():
             for gp in gpools:

@@ -144,6 +144,12 @@ int mvb_qk_norm_rope_kv_write(void* q, int64_t q_row_stride, void* k, int64_t k_
 size_t mvb_decode_workspace_bytes(int max_seqs, int num_q_heads, int head_dim);
 int mvb_decode_plan(const int32_t* cache_seqlens, int num_seqs, int window_left, int num_q_heads,
                     int num_kv_heads, int head_dim, void* workspace, size_t workspace_bytes, void* stream);
+/* Same plan, and the first block id of every CTA's range is looked up here once per step instead of by
+ * every layer's attention kernel in front of its first TMA load (the table must be the one passed to
+ * mvb_decode_attn). */
+int mvb_decode_plan_with_table(const int32_t* cache_seqlens, const int32_t* block_table, int64_t table_stride,
+                               int block_size, int num_seqs, int window_left, int num_q_heads, int num_kv_heads,
+                               int head_dim, void* workspace, size_t workspace_bytes, void* stream);
 int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
                     int64_t num_blocks, int block_size, const int32_t* cache_seqlens,
                     const int32_t* block_table, int64_t table_stride, int table_width, int num_seqs,

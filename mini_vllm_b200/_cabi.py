@@ -23,6 +23,7 @@ SIGNATURES = {
                                         i32, i32, i32, i32, i32, vp, vp]),
     "mvb_decode_workspace_bytes": (sz, [i32, i32, i32]),
     "mvb_decode_plan": (i32, [vp, i32, i32, i32, i32, i32, vp, sz, vp]),
+    "mvb_decode_plan_with_table": (i32, [vp, vp, i64, i32, i32, i32, i32, i32, i32, vp, sz, vp]),
     "mvb_decode_attn": (i32, [vp, i64, vp, vp, i64, i32, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, vp, i64,
                               vp, sz, vp, vp]),
     "mvb_decode_attn_static": (i32, [vp, i64, vp, vp, i64, i32, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, vp,

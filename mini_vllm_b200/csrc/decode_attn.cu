@@ -64,7 +64,7 @@ struct alignas(32) CtaDesc {
   int32_t tp0, tp1;           // that sequence's tile range
   int32_t n;                  // its context length
   int32_t per;                // tiles per CTA
-  int32_t pad;
+  int32_t blk0;               // block id holding tile t0 (-1: read it from the block table)
 };
 
 struct DecodeLayout {                  // byte offsets inside the workspace
@@ -111,6 +111,8 @@ __device__ __forceinline__ int visible_start(int n, int window_left) {
 __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int32_t* __restrict__ cache_seqlens,
                                                                    int num_seqs, int window_left, int cta_tokens,
                                                                    int num_ctas, int num_counters,
+                                                                   const int32_t* __restrict__ block_table,
+                                                                   int64_t table_stride, int block_size,
                                                                    DecodeHeader* hdr, CtaDesc* descs,
                                                                    int32_t* tile_prefix) {
   __shared__ int max_tiles_s;
@@ -143,7 +145,7 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int32_t
     CtaDesc d;
     d.t0 = t < total ? static_cast<int32_t>(t) : total;
     d.t1 = t + per < total ? static_cast<int32_t>(t + per) : total;
-    d.b = num_seqs; d.tp0 = d.tp1 = d.n = 0; d.per = per; d.pad = 0;
+    d.b = num_seqs; d.tp0 = d.tp1 = d.n = 0; d.per = per; d.blk0 = -1;
     if (t < total) {                   // last b with tile_prefix[b] <= t
       int lo = 0, hi = num_seqs;
       while (hi - lo > 1) {
@@ -151,6 +153,11 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int32_t
         if (tile_prefix[mid] <= t) lo = mid; else hi = mid;
       }
       d.b = lo; d.tp0 = tile_prefix[lo]; d.tp1 = tile_prefix[lo + 1]; d.n = cache_seqlens[lo];
+      if (block_table != nullptr) {      // spare the attention kernel one dependent load before its first TMA
+        const int start_al = visible_start(d.n, window_left) / cta_tokens * cta_tokens;
+        const int token0 = start_al + (static_cast<int>(t) - d.tp0) * cta_tokens;
+        d.blk0 = block_table[lo * table_stride + token0 / block_size];
+      }
     }
     descs[c] = d;
   }
@@ -213,7 +220,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     const int4* dp = reinterpret_cast<const int4*>(p.descs + c);
     const int4 lo = __ldg(dp), hi = __ldg(dp + 1);
     desc.t0 = lo.x; desc.t1 = lo.y; desc.b = lo.z; desc.tp0 = lo.w;
-    desc.tp1 = hi.x; desc.n = hi.y; desc.per = hi.z; desc.pad = hi.w;
+    desc.tp1 = hi.x; desc.n = hi.y; desc.per = hi.z; desc.blk0 = hi.w;
   }
   const int per = desc.per, t0 = desc.t0, t1 = desc.t1;
   // rows with an empty context (graph padding) produce zeros; spread over the CTAs, and done by
@@ -255,17 +262,24 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   };
   SeqView fs;
   seq_from_desc(fs);
-  int ft = t0, nfetch = 0, blk_base = -1, blk_reg = -1;
+  // lane i caches the block id of table column blk_base + i (blk_n valid lanes); seeded from the plan
+  int ft = t0, nfetch = 0, blk_base = -1, blk_reg = -1, blk_n = 0;
+  if (desc.blk0 >= 0) {
+    blk_base = (fs.start_al + (t0 - fs.tp0) * CT) / p.block_size;
+    blk_reg = desc.blk0;
+    blk_n = 1;
+  }
   auto fetch_next = [&]() -> bool {
     while (true) {
       if (ft >= t1) return false;
-      while (ft >= fs.tp1 && fs.b + 1 < p.num_seqs) { load_seq<CT>(fs, fs.b + 1, p); blk_base = -1; }
+      while (ft >= fs.tp1 && fs.b + 1 < p.num_seqs) { load_seq<CT>(fs, fs.b + 1, p); blk_base = -1; blk_n = 0; }
       const int token0 = fs.start_al + (ft - fs.tp0) * CT + sub * 16;
       ++ft;
       if (token0 >= fs.n || token0 + 16 <= fs.start) continue;
       const int bi = token0 / p.block_size;
-      if (blk_base < 0 || bi < blk_base || bi >= blk_base + 32) {
+      if (blk_base < 0 || bi < blk_base || bi >= blk_base + blk_n) {
         blk_base = bi;
+        blk_n = 32;
         const int col = bi + lane;
         blk_reg = col < p.table_width ? p.block_table[fs.b * p.table_stride + col] : -1;
       }
@@ -478,18 +492,19 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       // finds every partial of this sequence in memory and merges them
       __shared__ int is_last;
       const int c1 = cs.tp0 / per, c2 = (cs.tp1 - 1) / per;
-      __threadfence();
+      // the CTA barrier orders every thread's partial stores before thread 0's release; the last
+      // arriver's acquire plus its CTA barrier order them before every merging thread's loads
       __syncthreads();
       if (threadIdx.x == 0) {
         int32_t* cnt = p.arrivals + static_cast<int64_t>(b) * gridDim.y + blockIdx.y;
-        const int prev = atomicAdd(cnt, 1);
+        int prev;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(cnt) : "memory");
         is_last = (prev == c2 - c1);
         if (is_last) *cnt = 0;                               // re-arm for the next launch
       }
       __syncthreads();
       MVB_TRACE(7);
       if (is_last) {
-        __threadfence();
         constexpr int HEADS = HPC * 8;                       // upper bound of HPC * G
         constexpr int PC = 32;                               // partials weighted per pass
         constexpr int MAX_ITEMS = (HEADS * D / 4 + NW * 32 - 1) / (NW * 32);
@@ -613,9 +628,9 @@ static int decode_shape_ok(int hq, int hkv, int d) {
   return hkv % nw == 0;
 }
 
-extern "C" int mvb_decode_plan(const int32_t* cache_seqlens, int num_seqs, int window_left, int num_q_heads,
-                               int num_kv_heads, int head_dim, void* workspace, size_t workspace_bytes,
-                               void* stream) {
+static int decode_plan_impl(const int32_t* cache_seqlens, const int32_t* block_table, int64_t table_stride,
+                            int block_size, int num_seqs, int window_left, int num_q_heads, int num_kv_heads,
+                            int head_dim, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace mvb;
   if (!cache_seqlens || !workspace || num_seqs <= 0) return kInvalidArgument;
   if (!decode_shape_ok(num_q_heads, num_kv_heads, head_dim)) return kUnsupportedShape;
@@ -626,9 +641,25 @@ extern "C" int mvb_decode_plan(const int32_t* cache_seqlens, int num_seqs, int w
   if (num_ctas > kMaxCtas) num_ctas = kMaxCtas;
   decode_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       cache_seqlens, num_seqs, window_left, cta_tokens_for(num_kv_heads, head_dim), num_ctas,
-      num_seqs * num_q_heads, reinterpret_cast<DecodeHeader*>(ws), reinterpret_cast<CtaDesc*>(ws + l.descs),
-      reinterpret_cast<int32_t*>(ws + l.tile_prefix));
+      num_seqs * num_q_heads, block_table, table_stride, block_size, reinterpret_cast<DecodeHeader*>(ws),
+      reinterpret_cast<CtaDesc*>(ws + l.descs), reinterpret_cast<int32_t*>(ws + l.tile_prefix));
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+extern "C" int mvb_decode_plan(const int32_t* cache_seqlens, int num_seqs, int window_left, int num_q_heads,
+                               int num_kv_heads, int head_dim, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  return decode_plan_impl(cache_seqlens, nullptr, 0, 0, num_seqs, window_left, num_q_heads, num_kv_heads, head_dim,
+                          workspace, workspace_bytes, stream);
+}
+
+extern "C" int mvb_decode_plan_with_table(const int32_t* cache_seqlens, const int32_t* block_table,
+                                          int64_t table_stride, int block_size, int num_seqs, int window_left,
+                                          int num_q_heads, int num_kv_heads, int head_dim, void* workspace,
+                                          size_t workspace_bytes, void* stream) {
+  if (!block_table || block_size <= 0 || table_stride <= 0) return mvb::kInvalidArgument;
+  return decode_plan_impl(cache_seqlens, block_table, table_stride, block_size, num_seqs, window_left, num_q_heads,
+                          num_kv_heads, head_dim, workspace, workspace_bytes, stream);
 }
 
 extern "C" int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,

@@ -95,7 +95,8 @@ class FlashAttention(nn.Module):
         ws = ctx.decode_plans.get(wl)
         if ws is None:
             ws = _decode_workspace(q.device, ctx.cache_seqlens.numel(), self.num_heads, self.head_dim, wl)
-            ops.decode_plan(ctx.cache_seqlens, wl, self.num_heads, self.num_kv_heads, self.head_dim, ws)
+            ops.decode_plan(ctx.cache_seqlens, wl, self.num_heads, self.num_kv_heads, self.head_dim, ws,
+                            block_table=ctx.block_table, block_size=self.k_cache.shape[1])
             ctx.decode_plans[wl] = ws
         o = ops.decode_attn(q, self.k_cache, self.v_cache, ctx.cache_seqlens, ctx.block_table, self.scaling, wl, ws,
                             status=ctx.status)

@@ -187,10 +187,20 @@ def decode_workspace(max_seqs: int, num_q_heads: int, head_dim: int, device) -> 
 
 
 def decode_plan(cache_seqlens: torch.Tensor, window_left: int, num_q_heads: int, num_kv_heads: int,
-                head_dim: int, workspace: torch.Tensor) -> None:
+                head_dim: int, workspace: torch.Tensor, block_table: torch.Tensor | None = None,
+                block_size: int = 0) -> None:
+    """Plan the split of one decode step.  With ``block_table`` (the one the attention calls will get)
+    the plan also records each CTA's first block id, sparing every layer a dependent load."""
     _need(cache_seqlens, torch.int32, "cache_seqlens")
-    rc = _cabi.load().mvb_decode_plan(_ptr(cache_seqlens), cache_seqlens.numel(), window_left, num_q_heads,
-                                      num_kv_heads, head_dim, _ptr(workspace), workspace.numel(), _stream())
+    if block_table is not None:
+        _need(block_table, torch.int32, "block_table")
+        assert block_table.stride(1) == 1 and block_table.shape[0] >= cache_seqlens.numel() and block_size > 0
+        rc = _cabi.load().mvb_decode_plan_with_table(
+            _ptr(cache_seqlens), _ptr(block_table), block_table.stride(0), block_size, cache_seqlens.numel(),
+            window_left, num_q_heads, num_kv_heads, head_dim, _ptr(workspace), workspace.numel(), _stream())
+    else:
+        rc = _cabi.load().mvb_decode_plan(_ptr(cache_seqlens), cache_seqlens.numel(), window_left, num_q_heads,
+                                          num_kv_heads, head_dim, _ptr(workspace), workspace.numel(), _stream())
     _cabi.check(rc, "mvb_decode_plan")
     LaunchCounter.add(1)
 

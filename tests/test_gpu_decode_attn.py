@@ -25,7 +25,7 @@ def run_case(cuda, lens, hq, hkv, d, window_left=-1, seed=0, table_width=None, p
     status = ops.new_status(cuda)
     ws = ops.decode_workspace(B, hq, d, cuda)
     seqlens_d, bt_d = seqlens.to(cuda), bt.to(cuda)
-    ops.decode_plan(seqlens_d, window_left, hq, hkv, d, ws)
+    ops.decode_plan(seqlens_d, window_left, hq, hkv, d, ws, block_table=bt_d, block_size=256)
     out = torch.full((B, hq, d), float("nan"), dtype=torch.bfloat16, device=cuda)
     ops.decode_attn(q.to(cuda), k_pool.to(cuda), v_pool.to(cuda), seqlens_d, bt_d, d ** -0.5, window_left, ws,
                     out=out, status=status)
@@ -98,7 +98,7 @@ def test_graph_capture_and_replay(cuda):
     out = torch.zeros(B, hq, d, dtype=torch.bfloat16, device=cuda)
 
     def step():
-        ops.decode_plan(seqlens, -1, hq, hkv, d, ws)
+        ops.decode_plan(seqlens, -1, hq, hkv, d, ws, block_table=bt, block_size=256)
         ops.decode_attn(q_d, k_d, v_d, seqlens, bt, d ** -0.5, -1, ws, out=out)
 
     seqlens.copy_(torch.tensor(lens_a, dtype=torch.int32))
@@ -128,7 +128,7 @@ def test_bad_block_id_is_reported_not_fatal(cuda):
     bt = torch.tensor([[1, 99]], dtype=torch.int32, device=cuda)      # 99 is outside the 4-block pool
     status = ops.new_status(cuda)
     ws = ops.decode_workspace(1, hq, d, cuda)
-    ops.decode_plan(seqlens, -1, hq, hkv, d, ws)
+    ops.decode_plan(seqlens, -1, hq, hkv, d, ws, block_table=bt, block_size=256)
     ops.decode_attn(q, k_pool.to(cuda), v_pool.to(cuda), seqlens, bt, d ** -0.5, -1, ws, status=status)
     torch.cuda.synchronize()
     assert status[0].item() == 2
