@@ -3,12 +3,14 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
-Workload (``config.workload``): Qwen3-0.6B-shape random-init model, 64 requests per GPU with random
-token-id prompts, prompt lengths U[100,1024], output lengths U[100,1024] capped so prompt+output
-<= 1024, continuous batching, greedy decoding.  One "step" is one complete generation job over
-that request set.  At N > 1 each rank is an independent engine replica (no collective on the data
-path); the global request list of 64*N requests is partitioned by the host dispatcher by token
-count, so per-GPU work is fixed: weak scaling.
+Workload (``config.workload``): Qwen3-0.6B-shape random-init model, greedy decoding, continuous batching.
+Default: the per-GPU share of the box-scale offline-serving job the headline metric is quoted on
+(4096 requests over 8 GPUs = 512 requests per GPU, prompt lengths log-uniform [32,4096], output lengths
+U[64,1024], random token ids); ``--workload config2`` selects the 64-request job (prompt U[100,1024],
+prompt+output <= 1024).  One "step" is one complete generation job over the rank's request set.  At
+N > 1 each rank is an independent engine replica (no collective on the data path); the global list of
+512*N requests is partitioned by the host dispatcher by token count, so per-GPU work is fixed (weak
+scaling) and N = 8 is exactly the 4096-request job.
 
 Metric: prompt+generated tokens per second, whole job, all GPUs.
 * ``value``: the job's device time, CUDA events around its first and last kernel (the engine's step loop
@@ -45,8 +47,12 @@ from mini_vllm_b200.dispatcher import partition_by_tokens  # noqa: E402
 from mini_vllm_b200.workloads import (GEMMA3_1B, QWEN3_0P6B, config2_requests, config3, config4,  # noqa: E402
                                        decode_kv_bytes, prefill_flops)
 
-METRIC = "ragged prefill+decode tokens/s (Qwen3-0.6B shapes, 64 requests per GPU, greedy)"
-WORKLOAD = "config2: Qwen3-0.6B random-init, 64 req/GPU, prompt U[100,1024], total<=1024, continuous batching"
+METRIC = "ragged prefill+decode tokens/s (Qwen3-0.6B shapes, continuous batching, greedy)"
+WORKLOADS = {
+    "config5": "config5 share: Qwen3-0.6B random-init, 512 req/GPU (4096 over 8 GPUs), prompt log-U[32,4096], "
+               "output U[64,1024], continuous batching",
+    "config2": "config2: Qwen3-0.6B random-init, 64 req/GPU, prompt U[100,1024], total<=1024, continuous batching",
+}
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -93,11 +99,15 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------------
-def build_engine(local_rank: int):
+def build_engine(local_rank: int, workload: str = "config5"):
     from mini_vllm_b200.engine.engine import Engine
     torch.cuda.set_device(local_rank)
-    cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=512, max_num_batched_seqs=64,
-                 max_num_batched_tokens=16384, gpu_memory_utilization=0.5, use_cuda_graph=True, seed=0)
+    if workload == "config5":        # long prompts, hundreds of live sequences: a large pool, preemption allowed
+        cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=4096, max_num_batched_seqs=256,
+                     max_num_batched_tokens=16384, gpu_memory_utilization=0.85, use_cuda_graph=True, seed=0)
+    else:
+        cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=512, max_num_batched_seqs=64,
+                     max_num_batched_tokens=16384, gpu_memory_utilization=0.5, use_cuda_graph=True, seed=0)
     return Engine(cfg)
 
 
@@ -275,7 +285,7 @@ def kernel_extras(dev, peaks, nl=4):
 
 
 # ---- CPU leg: the oracle restatement of the reference path on the host cores ------------------------
-def cpu_reference_sample(budget_s: float = 20.0, seed: int = 0):
+def cpu_reference_sample(workload: str = "config5", budget_s: float = 20.0, seed: int = 0):
     """Prefill + decode of a few config-2 requests through the oracle model on CPU; returns tok/s."""
     from mini_vllm_b200.models.loader import load_model
     from mini_vllm_b200.engine.request import Request
@@ -284,14 +294,18 @@ def cpu_reference_sample(budget_s: float = 20.0, seed: int = 0):
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     hf = qwen3_shape()
-    cfg = Config(hf_config=hf, kv_cache_num_blocks=40, max_num_batched_seqs=8, use_cuda_graph=False, seed=seed)
+    cfg = Config(hf_config=hf, kv_cache_num_blocks=160, max_num_batched_seqs=8, use_cuda_graph=False, seed=seed)
     model = load_model(cfg, device="cpu")
     weights = reference_names(dict(model.state_dict()), "qwen3", hf)
     del model
-    omodel = OracleModel(weights, hf, "qwen3", 40, 256, device="cpu")
+    omodel = OracleModel(weights, hf, "qwen3", 160, 256, device="cpu")
     ex = OracleExecutor(omodel, 256)
     n_req, n_dec = 8, 48
-    reqs = config2_requests(seed)[:n_req]
+    if workload == "config5":
+        from mini_vllm_b200.workloads import config5_requests
+        reqs = config5_requests(seed, n=512)[:n_req]
+    else:
+        reqs = config2_requests(seed)[:n_req]
     sch = Scheduler(cfg)
     rs = [Request(r.prompt, SamplingParams(max_tokens=n_dec, ignore_eos=True)) for r in reqs]
     for r in rs:
@@ -315,13 +329,13 @@ def reference_arm(args):
         return
     vals = []
     for _ in range(max(1, min(args.steps, 3))):
-        v, threads, sample, dt = cpu_reference_sample()
+        v, threads, sample, dt = cpu_reference_sample(args.workload)
         vals.append(v)
     value = statistics.median(vals)
     line = {"impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD},
+            "config": {"workload": WORKLOADS[args.workload]},
             "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": threads, "kind": "port",
                              "sample": sample},
             "e2e": {"value": round(value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -336,6 +350,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="config5", choices=["config5", "config2"],
+                    help="config5 (default): 512 requests per GPU, prompts log-uniform [32,4096], outputs "
+                         "U[64,1024]; config2: 64 requests per GPU, prompt U[100,1024], total <= 1024")
     ap.add_argument("--kernel-legs", action="store_true",
                     help="profiling aid: only the fixed single-layer kernel cases (one 2.3 GB pool), then exit")
     ap.add_argument("--engine-steps", type=int, default=0,
@@ -372,9 +389,13 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks, peak_kind = measured_peaks()
 
-    all_reqs = config2_requests(seed=0, n=64 * world)
+    if args.workload == "config5":
+        from mini_vllm_b200.workloads import config5_requests
+        all_reqs = config5_requests(seed=0, n=512 * world)
+    else:
+        all_reqs = config2_requests(seed=0, n=64 * world)
     mine = [all_reqs[i] for i in partition_by_tokens([len(r.prompt) + r.max_tokens for r in all_reqs], world)[rank]]
-    engine = build_engine(local_rank)
+    engine = build_engine(local_rank, args.workload)
     dev = engine.executor.device
 
     def sync_all():
@@ -423,7 +444,7 @@ def main():
         extras = kernel_extras(dev, peaks)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            v, threads, sample, dt = cpu_reference_sample()
+            v, threads, sample, dt = cpu_reference_sample(args.workload)
             cpu = {"value": round(v, 2), "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample,
                    "seconds": round(dt, 1)}
         line = {
@@ -431,7 +452,7 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(cuda_ms_max / args.steps, 2), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "requests_per_gpu": len(mine), "parallelism": f"replicas x{world}",
+            "config": {"workload": WORKLOADS[args.workload], "requests_per_gpu": len(mine), "parallelism": f"replicas x{world}",
                        "l2": "KV pool (28 layers, >126 MB per step) exceeds L2; kernel legs rotate distinct pools",
                        "tokens_per_step_all_gpus": int(tok_all / args.steps)},
             "e2e": {"value": round(tok_all / (wall_ms_max * 1e-3), 1), "unit": "tokens/s",
