@@ -103,7 +103,9 @@ def build_engine(local_rank: int, workload: str = "config5"):
     from mini_vllm_b200.engine.engine import Engine
     torch.cuda.set_device(local_rank)
     if workload == "config5":        # long prompts, hundreds of live sequences: a large pool, preemption allowed
-        cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=4096, max_num_batched_seqs=256,
+        # up to 512 live sequences (the reference's default max_num_batched_seqs), all decode batches from graphs
+        cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=4096,
+                     max_num_batched_seqs=512, max_graph_batch_size=512,
                      max_num_batched_tokens=16384, gpu_memory_utilization=0.85, use_cuda_graph=True, seed=0)
     else:
         cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=512, max_num_batched_seqs=64,

@@ -37,6 +37,7 @@ class Config:
 
     # executor
     use_cuda_graph: bool = True
+    max_graph_batch_size: int = 256          # largest decode batch replayed from a CUDA graph (graph.py:11)
     seed: int = 0                            # weights of a random-init model and the sampler's stream
 
     def __post_init__(self):

@@ -20,7 +20,7 @@ class CudaGraphRunner:
     def __init__(self, model, config, max_batch_size: int, status: torch.Tensor | None = None):
         self.model = model
         self.config = config
-        self.max_batch_size = min(max_batch_size, 256)
+        self.max_batch_size = min(max_batch_size, getattr(config, "max_graph_batch_size", 256))
         sizes = [b for b in (1, 2, 4, 8) if b <= self.max_batch_size] + list(range(16, self.max_batch_size + 1, 16))
         self.batch_size_list = sorted(set(sizes + [self.max_batch_size]))   # the largest batch always has a graph
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
