@@ -210,19 +210,21 @@ int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void* k, int64_t
  * Fused temperature / top-k / Gumbel-max sampler over the vocabulary.
  * Replaces Sampler.forward (minivllm/models/layers/sampler.py:9-31).
  *   logits [num_rows, vocab] bf16 (row stride in elements) -> out int64 [num_rows].
- *   top_k == NULL: greedy argmax of logits / temperature (lowest index wins ties), the
+ *   top_k == NULL and top_p == NULL: greedy argmax of logits / temperature (lowest index wins ties), the
  *     reference's path when no top-k/top-p is requested (sampler.py:31).
- *   top_k != NULL: row r keeps every logit >= its top_k[r]-th largest (top_k[r] <= 0 keeps
- *     all), adds Gumbel noise from Philox4x32-10 keyed by (seed, offset, r, column) to
- *     logit / temperature, and returns the argmax.  temperatures may be NULL (all 1).
+ *   top_k != NULL or top_p != NULL: row r keeps every logit >= its top_k[r]-th largest
+ *     (top_k[r] <= 0 keeps all), then, if top_p[r] < 1, the most likely of those until their
+ *     softmax(logit / temperature) mass reaches top_p[r] (tokens tied with the last one are kept);
+ *     it adds Gumbel noise from Philox4x32-10 keyed by (seed, offset, r, column) to
+ *     logit / temperature and returns the argmax.  temperatures may be NULL (all 1).
  *   scatter_table/scatter_index (both or neither): the token of row r is also stored at
  *     scatter_table[scatter_index[r]], a per-request table the next decode packing reads its input
  *     tokens from (mvb_pack_decode's prev_sampled/src_index), so the sampled ids never have to visit
  *     the host between steps (the reference syncs on .tolist() every step, executor.py:193-195).
  */
 int mvb_sample(const void* logits, int64_t row_stride, int num_rows, int vocab, const float* temperatures,
-               const int32_t* top_k, uint64_t seed, uint64_t offset, int64_t* out, int64_t* scatter_table,
-               const int32_t* scatter_index, int32_t* dev_status, void* stream);
+               const int32_t* top_k, const float* top_p, uint64_t seed, uint64_t offset, int64_t* out,
+               int64_t* scatter_table, const int32_t* scatter_index, int32_t* dev_status, void* stream);
 
 /*
  * Decoder-layer glue around the attention path.  A decode step of a small model is bound by the number

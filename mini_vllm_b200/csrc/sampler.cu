@@ -3,7 +3,8 @@
 //
 // Greedy: argmax of float(logit) / T with the lowest index winning ties, which is what
 // torch.argmax returns on the same fp32 values.
-// Random: radix-select the k-th largest bf16 key with two 256-bin histogram passes, then
+// Random: radix-select the k-th largest bf16 key with two 256-bin histogram passes (and, for top-p, the
+// key at which the probability mass of the kept tokens reaches top_p, with two mass histograms), then
 // argmax over the kept entries of  logit / T - log(-log(u)),  u from Philox4x32-10 with
 // counter (column/4, row, offset_lo, offset_hi), key (seed_lo, seed_hi), word column%4.
 #include "common.cuh"
@@ -97,6 +98,7 @@ struct SampleParams {
   int vocab;
   const float* temperatures;
   const int32_t* top_k;
+  const float* top_p;
   uint64_t seed, offset;
   int64_t* out;
   int64_t* scatter_table;        // optional: table[scatter_index[row]] = token as well
@@ -124,13 +126,16 @@ __global__ void __launch_bounds__(kSampleThreads) sample_greedy_kernel(const Sam
 
 __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(const SampleParams p) {
   __shared__ uint32_t hist[256];
+  __shared__ float mass[256];
   __shared__ uint32_t sel_s[2];                              // selected bin, entries needed inside it
+  __shared__ float self_s[2];                                // nucleus: mass still needed, total mass
   const int r = blockIdx.x;
   const uint16_t* row = p.logits + r * p.row_stride;
   const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
   const float temp = p.temperatures != nullptr ? p.temperatures[r] : 1.f;
   const bool scaled = p.temperatures != nullptr;
-  const int k = p.top_k[r];
+  const int k = p.top_k != nullptr ? p.top_k[r] : 0;
+  const float top_p = p.top_p != nullptr ? p.top_p[r] : 1.f;
 
   uint32_t thresh = 0;                                       // keep keys >= thresh
   if (k > 0 && k < p.vocab) {
@@ -170,6 +175,69 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
     thresh = (hi_bin << 8) | sel_s[0];
   }
 
+  if (top_p < 1.f) {
+    // nucleus: the smallest set of the most likely kept tokens whose probability mass reaches top_p,
+    // found like the top-k threshold but with histograms of exp(x - max) instead of counts
+    Best mx{-INFINITY, 0x7fffffff};
+    for_each_logit(row, p.vocab, vec_ok, [&](int c, uint16_t bits) {
+      if (sort_key(bits) < thresh) return;
+      float x = bits_to_float(bits);
+      if (scaled) x = __fdiv_rn(x, temp);
+      if (better(x, c, mx.val, mx.idx)) { mx.val = x; mx.idx = c; }
+    });
+    mx = block_argmax(mx);
+    if (threadIdx.x == 0) self_s[1] = mx.val;
+    for (int i = threadIdx.x; i < 256; i += kSampleThreads) mass[i] = 0.f;
+    __syncthreads();
+    const float xmax = self_s[1];
+    __syncthreads();
+    auto weight = [&](uint16_t bits) {
+      float x = bits_to_float(bits);
+      if (scaled) x = __fdiv_rn(x, temp);
+      return expf(x - xmax);
+    };
+    for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) {
+      const uint32_t key = sort_key(bits);
+      if (key >= thresh) atomicAdd(&mass[key >> 8], weight(bits));
+    });
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float total = 0.f;
+      for (int i = 0; i < 256; ++i) total += mass[i];
+      float need = top_p * total;
+      uint32_t bin = thresh >> 8;
+      for (int i = 255; i >= static_cast<int>(thresh >> 8); --i) {
+        if (mass[i] >= need) { bin = i; break; }
+        need -= mass[i];
+      }
+      sel_s[0] = bin; self_s[0] = need;
+    }
+    __syncthreads();
+    const uint32_t hi_bin = sel_s[0];
+    const float need_hi = self_s[0];
+    __syncthreads();
+    for (int i = threadIdx.x; i < 256; i += kSampleThreads) mass[i] = 0.f;
+    __syncthreads();
+    for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) {
+      const uint32_t key = sort_key(bits);
+      if (key >= thresh && (key >> 8) == hi_bin) atomicAdd(&mass[key & 0xffu], weight(bits));
+    });
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float need = need_hi;
+      uint32_t bin = 0;
+      for (int i = 255; i >= 0; --i) {
+        if (mass[i] >= need && mass[i] > 0.f) { bin = i; break; }
+        need -= mass[i];
+      }
+      sel_s[0] = bin;
+    }
+    __syncthreads();
+    const uint32_t nucleus = (hi_bin << 8) | sel_s[0];
+    thresh = nucleus > thresh ? nucleus : thresh;
+    __syncthreads();
+  }
+
   const uint32_t k0 = static_cast<uint32_t>(p.seed), k1 = static_cast<uint32_t>(p.seed >> 32);
   const uint32_t o0 = static_cast<uint32_t>(p.offset), o1 = static_cast<uint32_t>(p.offset >> 32);
   Best b{-INFINITY, 0x7fffffff};
@@ -197,18 +265,18 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
 }  // namespace mvb
 
 extern "C" int mvb_sample(const void* logits, int64_t row_stride, int num_rows, int vocab,
-                          const float* temperatures, const int32_t* top_k, uint64_t seed, uint64_t offset,
-                          int64_t* out, int64_t* scatter_table, const int32_t* scatter_index, int32_t* dev_status,
+                          const float* temperatures, const int32_t* top_k, const float* top_p, uint64_t seed,
+                          uint64_t offset, int64_t* out, int64_t* scatter_table, const int32_t* scatter_index, int32_t* dev_status,
                           void* stream) {
   using namespace mvb;
   (void)dev_status;
   if (!logits || !out || num_rows < 0 || vocab <= 0 || row_stride < vocab) return kInvalidArgument;
   if ((scatter_table == nullptr) != (scatter_index == nullptr)) return kInvalidArgument;
   if (num_rows == 0) return kOk;
-  SampleParams p{static_cast<const uint16_t*>(logits), row_stride, vocab, temperatures, top_k, seed, offset, out,
-                 scatter_table, scatter_index};
+  SampleParams p{static_cast<const uint16_t*>(logits), row_stride, vocab, temperatures, top_k, top_p, seed, offset,
+                 out, scatter_table, scatter_index};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (top_k == nullptr) sample_greedy_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);
+  if (top_k == nullptr && top_p == nullptr) sample_greedy_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);
   else sample_topk_gumbel_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }

@@ -3,9 +3,9 @@
 ``forward(logits, temperatures, top_p, top_k)`` keeps the reference's parameter order.  Without
 top-k/top-p tensors the result is the greedy argmax of ``logits / temperature`` (the reference's
 behaviour: temperature alone never randomises, ``sampler.py:31``).  With ``top_k`` the kernel
-applies temperature, keeps each row's k largest logits and draws by Gumbel-max from a seeded
-Philox stream.  ``top_p`` is accepted for signature parity; nucleus filtering is not implemented
-and a request for it (any value < 1) raises.
+applies temperature, keeps each row's k largest logits, then the nucleus of probability mass
+``top_p`` among them, and draws by Gumbel-max from a seeded Philox stream (the reference hands both
+to flashinfer, swapped and unseeded, ``executor.py:195`` vs ``sampler.py:9-13``).
 """
 from __future__ import annotations
 
@@ -29,11 +29,9 @@ class Sampler(nn.Module):
                 ) -> torch.Tensor:
         if logits.dtype != torch.bfloat16:
             logits = logits.to(torch.bfloat16)
-        if top_p is not None and bool((top_p < 1.0).any()):
-            raise NotImplementedError("top-p sampling is not implemented; use top_k")
-        if top_k is None:
+        if top_k is None and top_p is None:
             return ops.sample(logits, temperatures, scatter_table=scatter_table, scatter_index=scatter_index)
-        out = ops.sample(logits, temperatures, top_k, self.seed, self.offset, scatter_table=scatter_table,
-                         scatter_index=scatter_index)
+        out = ops.sample(logits, temperatures, top_k, self.seed, self.offset, top_p=top_p,
+                         scatter_table=scatter_table, scatter_index=scatter_index)
         self.offset += 1
         return out

@@ -281,9 +281,9 @@ def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q
 
 
 def sample(logits: torch.Tensor, temperatures: torch.Tensor | None = None, top_k: torch.Tensor | None = None,
-           seed: int = 0, offset: int = 0, out: torch.Tensor | None = None,
+           seed: int = 0, offset: int = 0, out: torch.Tensor | None = None, top_p: torch.Tensor | None = None,
            scatter_table: torch.Tensor | None = None, scatter_index: torch.Tensor | None = None) -> torch.Tensor:
-    """logits bf16 [B,V] -> int64 [B].  top_k None: greedy; else temperature/top-k/Gumbel-max.
+    """logits bf16 [B,V] -> int64 [B].  top_k and top_p None: greedy; else temperature/top-k/top-p/Gumbel-max.
 
     With ``scatter_table`` (int64) and ``scatter_index`` (int32 [B]) the tokens are also written to
     ``scatter_table[scatter_index]`` on the device."""
@@ -299,7 +299,9 @@ def sample(logits: torch.Tensor, temperatures: torch.Tensor | None = None, top_k
     if scatter_table is not None:
         _need(scatter_table, torch.int64, "scatter_table"); _need(scatter_index, torch.int32, "scatter_index")
         assert scatter_index.numel() >= B
-    rc = _cabi.load().mvb_sample(_ptr(logits), logits.stride(0), B, V, _ptr(temperatures), _ptr(top_k),
+    if top_p is not None:
+        _need(top_p, torch.float32, "top_p")
+    rc = _cabi.load().mvb_sample(_ptr(logits), logits.stride(0), B, V, _ptr(temperatures), _ptr(top_k), _ptr(top_p),
                                  seed & (2**64 - 1), offset & (2**64 - 1), _ptr(out), _ptr(scatter_table),
                                  _ptr(scatter_index), None, _stream())
     _cabi.check(rc, "mvb_sample")

@@ -7,7 +7,8 @@ Greedy path (no top-k/top-p tensors): optional divide by temperature, then
 Random path: the reference hands the logits to flashinfer with top-k and top-p
 swapped (``executor.py:195`` vs ``sampler.py:9-13``) and without any seed, so it
 has no reproducible output to pin.  The intended semantics are implemented
-instead: temperature, keep every logit >= the k-th largest, then Gumbel-max
+instead: temperature, keep every logit >= the k-th largest, keep the smallest most-likely set whose
+softmax mass reaches top_p (ties with its last member included), then Gumbel-max
 with a counter-based Philox4x32-10 stream keyed by (seed, offset, row, column).
 """
 from __future__ import annotations
@@ -54,8 +55,9 @@ def greedy(logits: torch.Tensor, temperatures: torch.Tensor | None = None) -> to
 
 
 def gumbel_scores(logits: torch.Tensor, temperatures: torch.Tensor | None,
-                  top_k: torch.Tensor | None, seed: int, offset: int) -> torch.Tensor:
-    """fp32 ``[B,V]`` perturbed scores; entries outside the top-k set are -inf."""
+                  top_k: torch.Tensor | None, seed: int, offset: int,
+                  top_p: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 ``[B,V]`` perturbed scores; entries outside the top-k / top-p set are -inf."""
     x = logits.float()
     if temperatures is not None:
         x = x / temperatures.float().unsqueeze(-1)
@@ -65,6 +67,16 @@ def gumbel_scores(logits: torch.Tensor, temperatures: torch.Tensor | None,
             if 0 < k < v:
                 kth = torch.topk(x[r], k).values[-1]
                 x[r] = torch.where(x[r] >= kth, x[r], torch.full_like(x[r], float("-inf")))
+    if top_p is not None:
+        for r, pr in enumerate(top_p.tolist()):
+            if pr < 1.0:
+                keep = torch.isfinite(x[r])
+                probs = torch.softmax(x[r].double(), dim=-1)
+                order = torch.argsort(probs, descending=True, stable=True)
+                csum = torch.cumsum(probs[order], 0)
+                n_keep = int(torch.searchsorted(csum, torch.tensor(pr * float(csum[-1]), dtype=torch.float64))) + 1
+                cut = x[r][order[min(n_keep, v) - 1]]            # ties with the last kept token stay
+                x[r] = torch.where((x[r] >= cut) & keep, x[r], torch.full_like(x[r], float("-inf")))
     u = torch.from_numpy(uniform_open(seed, offset, b, v))
     return x - torch.log(-torch.log(u))
 

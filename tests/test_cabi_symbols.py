@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol_and_binding_covers_them():
 
 def test_host_only_calls_work_without_a_gpu():
     lib = _cabi.load()
-    assert lib.mvb_abi_version() == 2
+    assert lib.mvb_abi_version() == 3
     assert lib.mvb_status_string(0) == b"ok"
     assert b"scratch" in lib.mvb_status_string(-7)
     assert lib.mvb_decode_workspace_bytes(512, 16, 128) > 2 * 160 * 16 * 128 * 4
@@ -40,7 +40,7 @@ def test_host_only_calls_work_without_a_gpu():
     # argument errors are caught on the host before anything is launched
     assert lib.mvb_rope_kv_write(None, 0, None, 0, None, 0, None, None, 0, None, None, None, 0, 4, 2, 2, 100, 0,
                                  None, None) == -2          # head_dim not a multiple of 16
-    assert lib.mvb_sample(None, 0, 1, 10, None, None, 0, 0, None, None, None, None, None) == -1
+    assert lib.mvb_sample(None, 0, 1, 10, None, None, None, 0, 0, None, None, None, None, None) == -1
     assert lib.mvb_decode_plan(None, 1, -1, 16, 8, 128, None, 0, None) == -1
 
 

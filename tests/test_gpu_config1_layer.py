@@ -19,7 +19,8 @@ pytestmark = pytest.mark.gpu
 def test_config1_prefill_then_32_decode_steps(cuda):
     case, g = config1()
     hq, hkv, d, bs = 16, 8, 128, 256
-    lens, blocks = list(case.prefill_lens), case.prefill_blocks
+    lens, reserved = list(case.prefill_lens), case.prefill_blocks     # block lists sized for the 32 decode steps
+    held = lambda: [b[:-(-n // 256)] for n, b in zip(lens, reserved)]     # the blocks a sequence owns right now
     table = rope_kv.cos_sin_table(d, 4096, 1e6)
     table_d = table.to(cuda)
     kc_ref, vc_ref = torch.zeros(64, bs, hkv, d, dtype=torch.bfloat16), torch.zeros(64, bs, hkv, d, dtype=torch.bfloat16)
@@ -28,7 +29,7 @@ def test_config1_prefill_then_32_decode_steps(cuda):
 
     # ---- prefill
     tokens = [[0] * n for n in lens]
-    p = opack.build_prefill_input(tokens, blocks, [0] * 8, bs)
+    p = opack.build_prefill_input(tokens, held(), [0] * 8, bs)
     T = sum(lens)
     q, k, v = randn_bf16(g, T, hq, d), randn_bf16(g, T, hkv, d), randn_bf16(g, T, hkv, d)
     pos, slots, cu = torch.from_numpy(p["positions"]), torch.from_numpy(p["slot_mapping"]), torch.from_numpy(p["cu_seqlens_q"])
@@ -41,10 +42,10 @@ def test_config1_prefill_then_32_decode_steps(cuda):
     assert_close_attn(got, want, "config 1 prefill")
 
     # ---- 32 decode steps
-    bt = table_tensor(blocks)
     for step in range(32):
         lens = [n + 1 for n in lens]
-        pd = opack.build_decode_input([[0] * n for n in lens], blocks, bs)
+        bt = table_tensor(held())
+        pd = opack.build_decode_input([[0] * n for n in lens], held(), bs)
         q, k, v = randn_bf16(g, 8, hq, d), randn_bf16(g, 8, hkv, d), randn_bf16(g, 8, hkv, d)
         pos, slots = torch.from_numpy(pd["positions"]), torch.from_numpy(pd["slot_mapping"])
         seqlens = torch.from_numpy(pd["cache_seqlens"])
