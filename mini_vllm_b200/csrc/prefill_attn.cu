@@ -74,7 +74,7 @@ struct PrefillCfg {
   static constexpr int HALF_Q = 128 * 128;             // bytes of one 64-column half of a Q tile
   static constexpr int HALF_KV = BN * 128;             // bytes of one 64-column half of K / V
   static constexpr int SMEM = NQ * Q_BYTES + 4 * KV_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-  static constexpr int TMEM_COLS = 512;
+  static constexpr int TMEM_COLS = NQ * (BN + D) <= 256 ? 256 : 512;   // power of two; <= 256 lets two CTAs share an SM
   static constexpr int S_COL = 0;                      // S_t at S_COL + t * BN (P_t aliases its first BN/2 columns)
   static constexpr int O_COL = NQ * BN;                // O_t at O_COL + t * D
   static_assert(NQ * (BN + D) <= 512, "tensor memory budget");
@@ -485,10 +485,24 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   if (warp == NQ * 4 + 1) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
+struct PrefillOperands {            // what the tensor maps are built from
+  const void *q, *k, *v;
+  int64_t q_stride, k_stride, v_stride, kv_rows;
+  int total_q, hq, hkv;
+};
+
 template <int D, int BN, int NQ>
-static int launch_prefill(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
-                          int max_seqlen_q, cudaStream_t stream) {
+static int launch_prefill(const PrefillOperands& op, const PrefillParams& p, int max_seqlen_q, cudaStream_t stream) {
   using C = PrefillCfg<D, BN, NQ>;
+  if (p.block_table != nullptr && p.block_size % BN != 0) return kUnsupportedShape;   // a KV tile must not straddle blocks
+  // the TMA boxes are tied to the kernel's tile sizes: 128 query rows, BN key rows
+  CUtensorMap qm, km, vm;
+  int rc = make_kv_tensor_map(&qm, op.q, op.total_q, op.hq, D, op.q_stride, 128);
+  if (rc != kOk) return rc;
+  rc = make_kv_tensor_map(&km, op.k, op.kv_rows, op.hkv, D, op.k_stride, BN);
+  if (rc != kOk) return rc;
+  rc = make_kv_tensor_map(&vm, op.v, op.kv_rows, op.hkv, D, op.v_stride, BN);
+  if (rc != kOk) return rc;
   static bool configured_by_device[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -527,19 +541,12 @@ extern "C" int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void*
   if (num_seqs <= 0 || total_q < 0 || max_seqlen_q < 0 || kv_rows <= 0) return kInvalidArgument;
   if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return kInvalidArgument;
   if (head_dim != 128 && head_dim != 256) return kUnsupportedShape;
-  const int bn = head_dim == 128 ? 128 : 64;
-  if (block_table != nullptr && (block_size <= 0 || block_size % bn != 0)) return kUnsupportedShape;
+  if (block_table != nullptr && block_size <= 0) return kInvalidArgument;
   if (kv_rows > 0x7fffffffLL || num_seqs > 65535 || num_q_heads > 65535) return kUnsupportedShape;
   if (total_q == 0 || max_seqlen_q == 0) return kOk;
   if ((out_row_stride % 8) != 0 || !is_aligned(out, 16)) return kMisaligned;
 
-  CUtensorMap qm, km, vm;
-  int rc = make_kv_tensor_map(&qm, q, total_q, num_q_heads, head_dim, q_row_stride, 128);
-  if (rc != kOk) return rc;
-  rc = make_kv_tensor_map(&km, k, kv_rows, num_kv_heads, head_dim, k_row_stride, bn);
-  if (rc != kOk) return rc;
-  rc = make_kv_tensor_map(&vm, v, kv_rows, num_kv_heads, head_dim, v_row_stride, bn);
-  if (rc != kOk) return rc;
+  const PrefillOperands op{q, k, v, q_row_stride, k_row_stride, v_row_stride, kv_rows, total_q, num_q_heads, num_kv_heads};
 
   PrefillParams p;
   p.cu_q = cu_seqlens_q; p.cu_k = cu_seqlens_k; p.block_table = block_table; p.table_stride = table_stride;
@@ -551,6 +558,6 @@ extern "C" int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void*
   p.out = static_cast<__nv_bfloat16*>(out); p.out_stride = out_row_stride;
   p.dev_status = dev_status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (head_dim == 128) return launch_prefill<128, 128, 2>(qm, km, vm, p, max_seqlen_q, st);
-  return launch_prefill<256, 64, 1>(qm, km, vm, p, max_seqlen_q, st);
+  if (head_dim == 128) return launch_prefill<128, 128, 2>(op, p, max_seqlen_q, st);
+  return launch_prefill<256, 64, 1>(op, p, max_seqlen_q, st);
 }

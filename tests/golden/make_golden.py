@@ -30,7 +30,9 @@ import torch
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
 sys.path.insert(0, str(REPO))
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/mini-vllm   (a checkout of w4096/mini-vllm)")
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF))
 
 from oracle import attention as oattn  # noqa: E402  (the stub kernels the reference model runs around)

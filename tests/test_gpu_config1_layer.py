@@ -1,4 +1,4 @@
-"""BASELINE config 1, end to end at layer level: one Qwen3-0.6B attention layer, 8 sequences with prompt
+"""The single-layer correctness configuration, end to end at layer level: one Qwen3-0.6B attention layer, 8 sequences with prompt
 lengths U[16,512] (seed 0), 64-block pool, block tables from a seeded permutation; RoPE (theta 1e6) + KV write +
 causal varlen prefill, then 32 single-token decode steps with fresh N(0,1) q/k/v.  The attention layer (CUDA)
 runs next to the CPU oracle: outputs within tolerance at every step, KV pool bit-identical at the end."""
