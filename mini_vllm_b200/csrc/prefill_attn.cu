@@ -101,14 +101,17 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   // K/V tile loaded once serves them all: half the K/V traffic per flop) or, without a group to share,
   // NQ consecutive 128-row tiles of one head.
   const bool pair = p.pair_heads != 0;
-  const int s = blockIdx.y, qh0 = pair ? blockIdx.z * NQ : blockIdx.z;
+  // grid = (heads or head pairs, sequences, query-block rank): blocks are dispatched x-fastest, so every
+  // sequence's LAST query block (the one with the most keys) is handed out before any second-to-last one,
+  // which keeps the tail of the launch short
+  const int s = blockIdx.y, qh0 = pair ? blockIdx.x * NQ : blockIdx.x;
   const int kvh = qh0 / p.group;
   const int rows_per_cta = pair ? 128 : 128 * NQ;
   const int q0 = p.cu_q[s], q_len = p.cu_q[s + 1] - q0;
   const int k0 = p.cu_k[s], k_len = p.cu_k[s + 1] - k0;
   // longest blocks first: the last query block of a causal sequence has the most keys
   const int n_qb = (q_len + rows_per_cta - 1) / rows_per_cta;
-  const int qb = n_qb - 1 - static_cast<int>(blockIdx.x);
+  const int qb = n_qb - 1 - static_cast<int>(blockIdx.z);
   if (qb < 0) return;                                         // CTA-uniform
   const int row0 = qb * rows_per_cta;
   const int shift = k_len - q_len;                            // position of query row 0
@@ -515,7 +518,8 @@ static int launch_prefill(const PrefillOperands& op, const PrefillParams& p, int
   PrefillParams pp = p;
   pp.pair_heads = (NQ > 1 && p.group % NQ == 0) ? 1 : 0;
   const int rows_per_cta = pp.pair_heads ? 128 : 128 * NQ;
-  dim3 grid((max_seqlen_q + rows_per_cta - 1) / rows_per_cta, p.num_seqs, pp.pair_heads ? p.hq / NQ : p.hq);
+  dim3 grid(pp.pair_heads ? p.hq / NQ : p.hq, p.num_seqs, (max_seqlen_q + rows_per_cta - 1) / rows_per_cta);
+  if (grid.z > 65535) return kUnsupportedShape;
   prefill_attn_kernel<D, BN, NQ><<<grid, C::THREADS, C::SMEM, stream>>>(qm, km, vm, pp);
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
