@@ -1,11 +1,17 @@
 // Causal varlen prefill attention over dense or paged K/V on the tcgen05 tensor cores.
 //
-// One CTA owns NQ query tiles of 128 rows of one (sequence, query head) and walks the visible KV
-// tiles of BN tokens.  Warps are specialised:
-//   producer warp   TMA (128-byte swizzle, no multicast): the Q tiles once, then K and V tiles
-//                   through two-deep rings; KV tiles of the paged pool are addressed through the
-//                   block table (a tile never straddles a block); zero-fills V rows past the end
-//                   of the sequence (pool slots that were never written may hold NaNs);
+// A work item is NQ query tiles of 128 rows of one (sequence, query head or head pair); it walks the
+// visible KV tiles of BN tokens.  The grid has one block index per item, but a CTA does not end with
+// its item: through cluster launch control it takes over the index of a CTA that has not started yet
+// and carries on with its barriers, tensor memory and K/V rings alive, so the loads and first products
+// of the next item overlap the epilogue of the current one and nothing is set up twice.
+// Warps are specialised:
+//   producer warp   fetches items (skipping block indices past a sequence's last query block) and
+//                   publishes them to the other roles; TMA (128-byte swizzle, no multicast): the Q
+//                   tiles of an item, then K and V tiles through two-deep rings; KV tiles of the
+//                   paged pool are addressed through the block table (a tile never straddles a
+//                   block); zero-fills V rows past the end of the sequence (pool slots that were
+//                   never written may hold NaNs);
 //   MMA warp        one thread issues every tcgen05.mma: S_t = Q_t K^T (M=128, N=BN, fp32
 //                   accumulators in tensor memory) and O_t += P_t V with P read from tensor
 //                   memory (it overwrites S in place as packed bf16) and V consumed MN-major
@@ -17,7 +23,9 @@
 //                   memory, O rescaled in tensor memory only when the running max moved by more
 //                   than 2^8 (the stale max is carried exactly through P and the row sum), and the
 //                   epilogue O / l -> bf16 -> global.
-// Every mbarrier wait is bounded; a wait that gives up poisons the CTA, which then drains.
+// Every barrier is used round after round across items; each role keeps its own counters and derives
+// the parity it waits for from them.  Every mbarrier wait is bounded; a wait that gives up poisons
+// the CTA, which then drains (and stops taking items).
 //
 // Roofline: tensor-bound, 4 * D flops per (query, key) pair per head.
 #include "common.cuh"
@@ -28,26 +36,21 @@
 
 namespace mvb {
 
-// Optional phase timers (only with -DMVB_PREFILL_TRACE): one CTA accumulates SM-clock deltas per
-// phase in registers and writes them once at the end.
-#ifdef MVB_PREFILL_TRACE
-__device__ unsigned long long* g_prefill_trace = nullptr;
-#define MVB_PT_DECL long long pt_acc_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long pt_last_ = clock64();
-#define MVB_PTRACE(role, it, code)                                   \
-  do {                                                               \
-    const long long now_ = clock64();                                \
-    pt_acc_[(code)] += now_ - pt_last_;                              \
-    pt_last_ = now_;                                                 \
-  } while (0)
-#define MVB_PT_FLUSH(role)                                                                        \
-  do {                                                                                            \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && g_prefill_trace)                 \
-      for (int i_ = 0; i_ < 8; ++i_) g_prefill_trace[(role) * 8 + i_] = pt_acc_[i_];              \
+// Optional event log (only with -DMVB_PREFILL_EVLOG): the CTA that starts on block (0,0,0) appends
+// (code, SM clock) pairs per role to a caller-provided buffer of 4 x 512 words.
+#ifdef MVB_PREFILL_EVLOG
+__device__ unsigned long long* g_prefill_evlog = nullptr;
+#define MVB_EV_DECL(role, on) int ev_n_ = 0; const int ev_role_ = (role); \
+  const bool ev_on_ = (on) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && g_prefill_evlog != nullptr;
+#define MVB_EV(code)                                                                               \
+  do {                                                                                             \
+    if (ev_on_ && ev_n_ < 512)                                                                     \
+      g_prefill_evlog[ev_role_ * 512 + ev_n_++] =                                                  \
+          (static_cast<unsigned long long>(code) << 48) | (static_cast<unsigned long long>(clock64()) & 0xffffffffffffULL); \
   } while (0)
 #else
-#define MVB_PT_DECL
-#define MVB_PTRACE(role, it, code)
-#define MVB_PT_FLUSH(role)
+#define MVB_EV_DECL(role, on)
+#define MVB_EV(code)
 #endif
 
 struct PrefillParams {
@@ -58,13 +61,20 @@ struct PrefillParams {
   int block_size;
   int64_t kv_rows;
   int num_seqs, hq, group;
-  int pair_heads;               // 1: the CTA's query tiles are the heads of one GQA group over the same rows
+  int pair_heads;               // 1: an item's query tiles are the heads of one GQA group over the same rows
   float scale_log2;
   int window_left;
   __nv_bfloat16* out;
   int64_t out_stride;
   int* dev_status;
 };
+
+// barrier slots
+// P is published in 64-key halves (slot B_PFULL + 2 * tile + half) so the PV product of the first
+// half starts while the second half is still being exponentiated.
+enum : int { B_QFULL = 0, B_KFULL = 2, B_VFULL = 4, B_KFREE = 6, B_VFREE = 8, B_SFULL = 10, B_PFULL = 12,
+             B_ODONE = 16, B_OFREE = 18, B_VFIXED = 20, B_QFREE = 21, B_ITEM_FULL = 22, B_ITEM_FREE = 24,
+             B_CLC = 26, B_COUNT = 27 };
 
 template <int D, int BN, int NQ>
 struct PrefillCfg {
@@ -73,77 +83,107 @@ struct PrefillCfg {
   static constexpr int KV_BYTES = BN * D * 2;          // one K (or V) tile
   static constexpr int HALF_Q = 128 * 128;             // bytes of one 64-column half of a Q tile
   static constexpr int HALF_KV = BN * 128;             // bytes of one 64-column half of K / V
-  static constexpr int SMEM = NQ * Q_BYTES + 4 * KV_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-  static constexpr int TMEM_COLS = NQ * (BN + D) <= 256 ? 256 : 512;   // power of two; <= 256 lets two CTAs share an SM
+  // after the tiles: barriers, the tensor-memory address, the failure flag, two item slots and the
+  // launch-control response
+  static constexpr int CTRL_BYTES = 512;
+  static constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_FAIL = OFF_TMEM_SLOT + 4, OFF_ITEMS = 224, OFF_CLC = 256;
+  static constexpr int STAGE_BYTES = NQ * 4 * 4096;     // a 32-row x 128-byte output staging tile per softmax warp
+  static constexpr int SMEM = NQ * Q_BYTES + 4 * KV_BYTES + 1024 /*align*/ + CTRL_BYTES + STAGE_BYTES;
+  static constexpr int TMEM_COLS = NQ * (BN + D) <= 256 ? 256 : 512;   // power of two
   static constexpr int S_COL = 0;                      // S_t at S_COL + t * BN (P_t aliases its first BN/2 columns)
   static constexpr int O_COL = NQ * BN;                // O_t at O_COL + t * D
   static_assert(NQ * (BN + D) <= 512, "tensor memory budget");
   static_assert(BN % 64 == 0, "P is written in 64-key halves");
+  static_assert(OFF_FAIL + 4 <= OFF_ITEMS && OFF_CLC + 16 <= CTRL_BYTES, "control block layout");
 };
 
-// barrier slots
-// P is published in 64-key halves (slot B_PFULL + 2 * tile + half) so the PV product of the first
-// half starts while the second half is still being exponentiated.
-enum : int { B_QFULL = 0, B_KFULL = 2, B_VFULL = 4, B_KFREE = 6, B_VFREE = 8, B_SFULL = 10, B_PFULL = 12,
-             B_ODONE = 16, B_VFIXED = 18, B_COUNT = 19 };
+// What every role derives from an item's block index.
+template <int BN, int NQ>
+struct PrefillItem {
+  int s, q0, k0, k_len, row0, kvh;
+  int rows[NQ], pf[NQ], pl[NQ], jlo[NQ], jhi[NQ], roff[NQ], head[NQ];
+  int j_lo, j_hi, n_it;
+  bool empty;                                          // block index past the sequence's last query block
+
+  // grid = (heads or head pairs, sequences, query-block rank counted from the END of the sequence):
+  // indices are handed out x-fastest, so every sequence's last query block (the one with the most
+  // keys) is worked on before any second-to-last one, which keeps the tail of the launch short
+  __device__ __forceinline__ void init(const PrefillParams& p, int bx, int by, int bz) {
+    const bool pair = p.pair_heads != 0;
+    // The NQ query tiles of an item are either NQ heads of one GQA group over the same 128 rows (each
+    // K/V tile loaded once serves them all: half the K/V traffic per flop) or, without a group to
+    // share, NQ consecutive 128-row tiles of one head.
+    s = by;
+    const int qh0 = pair ? bx * NQ : bx;
+    kvh = qh0 / p.group;
+    const int rows_per_item = pair ? 128 : 128 * NQ;
+    q0 = p.cu_q[s];
+    k0 = p.cu_k[s];
+    const int q_len = p.cu_q[s + 1] - q0;
+    k_len = p.cu_k[s + 1] - k0;
+    const int n_qb = (q_len + rows_per_item - 1) / rows_per_item;
+    const int qb = n_qb - 1 - bz;
+    empty = qb < 0;
+    row0 = qb * rows_per_item;
+    const int shift = k_len - q_len;                   // position of query row 0
+    j_lo = 0x7fffffff;
+    j_hi = -1;
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) {
+      roff[t] = pair ? 0 : 128 * t;
+      head[t] = pair ? qh0 + t : qh0;
+      rows[t] = empty ? 0 : max(0, min(128, q_len - row0 - roff[t]));
+      pf[t] = shift + row0 + roff[t];
+      pl[t] = pf[t] + rows[t] - 1;
+      jlo[t] = p.window_left >= 0 ? max(0, pf[t] - p.window_left) / BN : 0;
+      jhi[t] = rows[t] > 0 ? pl[t] / BN : -1;
+      if (rows[t] > 0) { j_lo = min(j_lo, jlo[t]); j_hi = max(j_hi, jhi[t]); }
+    }
+    n_it = j_hi - j_lo + 1;
+    if (n_it <= 0) empty = true;
+  }
+};
 
 template <int D, int BN, int NQ>
 __global__ void __launch_bounds__(PrefillCfg<D, BN, NQ>::THREADS, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const PrefillParams p) {
   using C = PrefillCfg<D, BN, NQ>;
+  using Item = PrefillItem<BN, NQ>;
   constexpr uint32_t IDESC_S = umma_idesc_bf16(128, BN, false, false);
   constexpr uint32_t IDESC_O = umma_idesc_bf16(128, D, false, true);
   extern __shared__ uint8_t smem_raw[];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // The NQ query tiles of a CTA are either NQ heads of one GQA group over the same 128 rows (each
-  // K/V tile loaded once serves them all: half the K/V traffic per flop) or, without a group to share,
-  // NQ consecutive 128-row tiles of one head.
-  const bool pair = p.pair_heads != 0;
-  // grid = (heads or head pairs, sequences, query-block rank): blocks are dispatched x-fastest, so every
-  // sequence's LAST query block (the one with the most keys) is handed out before any second-to-last one,
-  // which keeps the tail of the launch short
-  const int s = blockIdx.y, qh0 = pair ? blockIdx.x * NQ : blockIdx.x;
-  const int kvh = qh0 / p.group;
-  const int rows_per_cta = pair ? 128 : 128 * NQ;
-  const int q0 = p.cu_q[s], q_len = p.cu_q[s + 1] - q0;
-  const int k0 = p.cu_k[s], k_len = p.cu_k[s + 1] - k0;
-  // longest blocks first: the last query block of a causal sequence has the most keys
-  const int n_qb = (q_len + rows_per_cta - 1) / rows_per_cta;
-  const int qb = n_qb - 1 - static_cast<int>(blockIdx.z);
-  if (qb < 0) return;                                         // CTA-uniform
-  const int row0 = qb * rows_per_cta;
-  const int shift = k_len - q_len;                            // position of query row 0
-
-  // per query tile: rows, first/last position, KV tile range
-  int rows_t[NQ], pf_t[NQ], pl_t[NQ], jlo_t[NQ], jhi_t[NQ], roff_t[NQ], head_t[NQ];
-  int j_lo = 0x7fffffff, j_hi = -1;
-#pragma unroll
-  for (int t = 0; t < NQ; ++t) {
-    roff_t[t] = pair ? 0 : 128 * t;
-    head_t[t] = pair ? qh0 + t : qh0;
-    rows_t[t] = max(0, min(128, q_len - row0 - roff_t[t]));
-    pf_t[t] = shift + row0 + roff_t[t];
-    pl_t[t] = pf_t[t] + rows_t[t] - 1;
-    jlo_t[t] = p.window_left >= 0 ? max(0, pf_t[t] - p.window_left) / BN : 0;
-    jhi_t[t] = rows_t[t] > 0 ? pl_t[t] / BN : -1;
-    if (rows_t[t] > 0) { j_lo = min(j_lo, jlo_t[t]); j_hi = max(j_hi, jhi_t[t]); }
+  {
+    // a CTA whose own index is past its sequence's last query block has nothing to set up; the indices
+    // still pending are taken by the CTAs that are at work
+    Item own;
+    own.init(p, blockIdx.x, blockIdx.y, blockIdx.z);
+    if (own.empty) return;                                    // CTA-uniform
   }
-  const int n_it = j_hi - j_lo + 1;
-  auto active = [&](int t, int j) { return rows_t[t] > 0 && j >= jlo_t[t] && j <= jhi_t[t]; };
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_s = base;                                  // NQ tiles
   const uint32_t k_s = q_s + NQ * C::Q_BYTES;                 // 2 stages
   const uint32_t v_s = k_s + 2 * C::KV_BYTES;                 // 2 stages
-  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + NQ * C::Q_BYTES + 4 * C::KV_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
-  volatile uint32_t* fail_flag = tmem_slot + 1;
+  uint8_t* ctrl = base_ptr + NQ * C::Q_BYTES + 4 * C::KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + C::OFF_TMEM_SLOT);
+  volatile uint32_t* fail_flag = reinterpret_cast<uint32_t*>(ctrl + C::OFF_FAIL);
+  volatile int4* items = reinterpret_cast<volatile int4*>(ctrl + C::OFF_ITEMS);   // {x, y, z, valid}
+  const uint32_t clc_resp = smem_u32(ctrl + C::OFF_CLC);
+  const uint32_t stage_s = smem_u32(ctrl + C::CTRL_BYTES);
 
   if (tid == 0) {
-    for (int i = 0; i < B_COUNT; ++i) mbar_init(&bars[i], (i >= B_PFULL && i < B_PFULL + 4) ? 128u : 1u);
+    for (int i = 0; i < B_COUNT; ++i) {
+      uint32_t count = 1u;
+      if (i >= B_PFULL && i < B_PFULL + 4) count = 4u;          // one lane per softmax warp
+      if (i >= B_OFREE && i < B_OFREE + 2) count = 4u;
+      if (i >= B_ITEM_FREE && i < B_ITEM_FREE + 2) count = 1u + NQ * 128u;
+      mbar_init(&bars[i], count);
+    }
     *fail_flag = 0;
     fence_mbar_init();
   }
@@ -166,18 +206,35 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     *fail_flag = 1;
     return false;
   };
+  // The consumer side of the item ring: false at the end of the work (or on failure).
+  auto next_item = [&](uint32_t n, Item& item) -> bool {
+    const int slot = n & 1;
+    if (!wait(B_ITEM_FULL + slot, (n >> 1) & 1, 900)) return false;
+    const int x = items[slot].x, y = items[slot].y, z = items[slot].z, valid = items[slot].w;
+    mbar_arrive(&bars[B_ITEM_FREE + slot]);
+    if (!valid) return false;
+    item.init(p, x, y, z);
+    return true;
+  };
 
   if (warp == NQ * 4) {
     // ============================ producer warp ======================================================
-    auto kv_row = [&](int j) -> int {                         // tensor-map row of KV tile j of this sequence
-      const int tok = j * BN;
-      if (p.block_table == nullptr) return k0 + tok;
-      const int blk = p.block_table[s * p.table_stride + tok / p.block_size];
-      if (blk < 0 || static_cast<int64_t>(blk + 1) * p.block_size > p.kv_rows) {
-        report(p.dev_status, kDevBadBlock, s);
-        return -BN;                                           // fully out of range: zero fill
+    // All lanes walk the items together (the zero fill is warp-wide); lane 0 owns barriers and TMA.
+    Item item;
+    int bx = blockIdx.x, by = blockIdx.y, bz = blockIdx.z;
+    uint32_t n_pub = 0, n_clc = 0, g = 0;                     // items published, responses read, KV tiles loaded
+    uint32_t k_issued = 0, v_issued = 0;                      // lane 0: K / V tile loads handed to TMA
+    bool clc_pending = false;                                 // lane 0: a request whose response has not been read
+    bool ok = true, have = true;
+    MVB_EV_DECL(0, lane == 0)
+    if (lane == 0) { tma_prefetch_desc(&q_map); tma_prefetch_desc(&k_map); tma_prefetch_desc(&v_map); }
+    auto publish = [&](int x, int y, int z, int valid) {      // lane 0
+      const int slot = n_pub & 1;
+      if (n_pub >= 2) ok = wait(B_ITEM_FREE + slot, ((n_pub >> 1) - 1) & 1, 910);
+      if (ok) {
+        items[slot].x = x; items[slot].y = y; items[slot].z = z; items[slot].w = valid;
+        mbar_arrive(&bars[B_ITEM_FULL + slot]);
       }
-      return blk * p.block_size + tok % p.block_size;
     };
     auto load_tile = [&](const CUtensorMap* map, uint32_t dst, uint64_t* bar, int z) {
       mbar_arrive_expect_tx(bar, C::KV_BYTES);
@@ -186,57 +243,119 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         asm volatile(
             "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
             ::"r"(dst + h * C::HALF_KV), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(h * 64),
-              "r"(kvh), "r"(z) : "memory");
+              "r"(item.kvh), "r"(z) : "memory");
       }
     };
-    if (lane == 0) {
-      tma_prefetch_desc(&q_map); tma_prefetch_desc(&k_map); tma_prefetch_desc(&v_map);
-#pragma unroll
-      for (int t = 0; t < NQ; ++t) {
-        if (rows_t[t] <= 0) continue;
-        mbar_arrive_expect_tx(&bars[B_QFULL + t], C::Q_BYTES);
-#pragma unroll
-        for (int h = 0; h < D / 64; ++h) {
-          asm volatile(
-              "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-              ::"r"(q_s + t * C::Q_BYTES + h * C::HALF_Q), "l"(reinterpret_cast<uint64_t>(&q_map)),
-                "r"(smem_u32(&bars[B_QFULL + t])), "r"(h * 64), "r"(head_t[t]), "r"(q0 + row0 + roff_t[t]) : "memory");
-        }
+    auto kv_row = [&](int j) -> int {                         // tensor-map row of KV tile j of this sequence
+      const int tok = j * BN;
+      if (p.block_table == nullptr) return item.k0 + tok;
+      const int blk = p.block_table[item.s * p.table_stride + tok / p.block_size];
+      if (blk < 0 || static_cast<int64_t>(blk + 1) * p.block_size > p.kv_rows) {
+        report(p.dev_status, kDevBadBlock, item.s);
+        return -BN;                                           // fully out of range: zero fill
       }
-    }
-    bool ok = true;
-    MVB_PT_DECL
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int st = it & 1, j = j_lo + it;
+      return blk * p.block_size + tok % p.block_size;
+    };
+    while (ok && have) {
+      MVB_EV(10);
+      item.init(p, bx, by, bz);
+      MVB_EV(item.empty ? 19 : 11);
       if (lane == 0) {
-        const int z = kv_row(j);
-        if (it >= 2) ok = wait(B_KFREE + st, ((it >> 1) - 1) & 1, 100 + it);
-        if (ok) load_tile(&k_map, k_s + st * C::KV_BYTES, &bars[B_KFULL + st], z);
-        MVB_PTRACE(0, it, 0);
-        if (ok && it >= 2) ok = wait(B_VFREE + st, ((it >> 1) - 1) & 1, 200 + it);
-        if (ok) load_tile(&v_map, v_s + st * C::KV_BYTES, &bars[B_VFULL + st], z);
-        MVB_PTRACE(0, it, 1);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      const int valid = k_len - j * BN;
-      if (ok && valid < BN) {                                 // last, partial tile: zero V rows past the end
-        ok = wait(B_VFULL + st, (it >> 1) & 1, 300 + it);
-        if (ok) {
-          for (int r = max(valid, 0) + lane; r < BN; r += 32) {
-#pragma unroll
-            for (int h = 0; h < D / 64; ++h)
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_s + st * C::KV_BYTES + h * C::HALF_KV + r * 128 + q * 16),
-                             "r"(0) : "memory");
-          }
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars[B_VFIXED]);
+        if (!item.empty) publish(bx, by, bz, 1);
+        MVB_EV(12);
+        if (ok) {                                             // ask for the next index while this one is worked on
+          fence_proxy_async();                                // the response slot was last read with ordinary loads
+          mbar_arrive_expect_tx(&bars[B_CLC], 16);
+          clc_try_cancel(clc_resp, &bars[B_CLC]);
+          clc_pending = true;
         }
       }
+      if (!item.empty) {
+        if (lane == 0 && ok) {
+          // the Q tiles are single-buffered: every S product of the previous item must have read them
+          if (n_pub >= 1) ok = wait(B_QFREE, (n_pub - 1) & 1, 920);
+          MVB_EV(13);
+#pragma unroll
+          for (int t = 0; t < NQ; ++t) {
+            if (!ok || item.rows[t] <= 0) continue;
+            mbar_arrive_expect_tx(&bars[B_QFULL + t], C::Q_BYTES);
+#pragma unroll
+            for (int h = 0; h < D / 64; ++h) {
+              asm volatile(
+                  "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                  ::"r"(q_s + t * C::Q_BYTES + h * C::HALF_Q), "l"(reinterpret_cast<uint64_t>(&q_map)),
+                    "r"(smem_u32(&bars[B_QFULL + t])), "r"(h * 64), "r"(item.head[t]),
+                    "r"(item.q0 + item.row0 + item.roff[t]) : "memory");
+            }
+          }
+        }
+        ++n_pub;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        for (int it = 0; it < item.n_it && ok; ++it, ++g) {
+          const int st = g & 1, j = item.j_lo + it;
+          const uint32_t ring_parity = (g >> 1) & 1;
+          if (lane == 0) {
+            const int z = kv_row(j);
+            if (g >= 2) ok = wait(B_KFREE + st, ring_parity ^ 1, 100);
+            if (ok) { load_tile(&k_map, k_s + st * C::KV_BYTES, &bars[B_KFULL + st], z); ++k_issued; }
+            MVB_EV(15);
+            if (ok && g >= 2) ok = wait(B_VFREE + st, ring_parity ^ 1, 200);
+            if (ok) { load_tile(&v_map, v_s + st * C::KV_BYTES, &bars[B_VFULL + st], z); ++v_issued; }
+            MVB_EV(16);
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          const int valid = item.k_len - j * BN;
+          if (ok && valid < BN) {                             // last, partial tile: zero V rows past the end
+            ok = __all_sync(0xffffffffu, wait(B_VFULL + st, ring_parity, 300));
+            if (ok) {
+              for (int r = max(valid, 0) + lane; r < BN; r += 32) {
+#pragma unroll
+                for (int h = 0; h < D / 64; ++h)
+#pragma unroll
+                  for (int q = 0; q < 8; ++q)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_s + st * C::KV_BYTES + h * C::HALF_KV + r * 128 + q * 16),
+                                 "r"(0) : "memory");
+              }
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&bars[B_VFIXED]);
+            }
+          }
+        }
+      }
+      // the next index (or the end of the work)
+      int nx = 0, ny = 0, nz = 0, more = 0;
+      if (lane == 0 && ok) {
+        MVB_EV(17);
+        ok = wait(B_CLC, n_clc & 1, 930);
+        MVB_EV(18);
+        if (ok) {
+          clc_pending = false;
+          more = clc_query(clc_resp, nx, ny, nz) ? 1 : 0;
+          if (more && (nx >= static_cast<int>(gridDim.x) || ny >= static_cast<int>(gridDim.y) ||
+                       nz >= static_cast<int>(gridDim.z))) {
+            report(p.dev_status, kDevWaitTimeout, 931);       // an index outside the grid: stop taking items
+            *fail_flag = 1;
+            ok = false;
+          }
+        }
+      }
+      ++n_clc;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      have = __shfl_sync(0xffffffffu, more, 0) != 0;
+      bx = __shfl_sync(0xffffffffu, nx, 0);
+      by = __shfl_sync(0xffffffffu, ny, 0);
+      bz = __shfl_sync(0xffffffffu, nz, 0);
     }
-    if (lane == 0) { MVB_PT_FLUSH(0); }
+    if (lane == 0 && ok) publish(0, 0, 0, 0);                 // end of the work
+    if (lane == 0 && !ok) {
+      // poisoned: nothing asynchronous may still be writing this CTA's shared memory when it ends
+      if (clc_pending) mbar_wait(&bars[B_CLC], n_clc & 1);
+      for (uint32_t back = 1; back <= 2; ++back) {
+        if (k_issued >= back) mbar_wait(&bars[B_KFULL + ((k_issued - back) & 1)], ((k_issued - back) >> 1) & 1);
+        if (v_issued >= back) mbar_wait(&bars[B_VFULL + ((v_issued - back) & 1)], ((v_issued - back) >> 1) & 1);
+      }
+    }
   } else if (warp == NQ * 4 + 1) {
     // ============================ MMA warp (one issuing thread) ======================================
     // This thread shares its scheduler with two softmax warps that always have work, so every
@@ -244,13 +363,14 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     // are compile-time constants and a wait is one try_wait unless the barrier is really not ready.
     if (lane == 0) {
       bool ok = true;
-      MVB_PT_DECL
       const uint64_t q_desc0 = umma_desc_sw128(q_s, 16, 1024);
       const uint64_t k_desc0 = umma_desc_sw128(k_s, 16, 1024);
       const uint64_t v_desc0 = umma_desc_sw128(v_s, C::HALF_KV, 1024);
-      const int jlo0 = jlo_t[0], jhi0 = jhi_t[0];
-      const int jlo1 = jlo_t[NQ - 1], jhi1 = jhi_t[NQ - 1];   // tile NQ-1 (== tile 0 when NQ == 1)
-      const int j_partial = k_len / BN;                       // first KV tile with rows past the end
+      uint32_t g = 0;                                         // KV tiles consumed (ring position)
+      uint32_t n_pv[2] = {0, 0};                              // PV products issued per query tile (P parity)
+      uint32_t n_act[2] = {0, 0};                             // items in which the query tile had rows (Q / O parity)
+      uint32_t n_fixed = 0;                                   // partial V tiles seen
+      int jlo0 = 0, jhi0 = -1, jlo1 = 0, jhi1 = -1, j_lo = 0, j_partial = 0;
       auto ready = [&](int slot, uint32_t parity, int where) -> bool {
         return mbar_try_wait(&bars[slot], parity) ? true : wait(slot, parity, where);
       };
@@ -264,222 +384,322 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         }
         umma_commit(&bars[B_SFULL + t]);
       };
-      // O_t (+)= P_t . V for KV tile j: V must have landed (and been fixed up if partial); the halves
-      // of P_t are consumed as the softmax group publishes them
-      auto pv_step = [&](auto tt, int it, bool v_known) {
+      // O_t (+)= P_t . V for the KV tile at ring position gk (tile j of the sequence): V must have
+      // landed (and been fixed up if partial); the halves of P_t are consumed as the softmax group
+      // publishes them.  The first product of an item overwrites O_t, which the previous item's
+      // epilogue must have read out.
+      auto pv_step = [&](auto tt, uint32_t gk, int j, bool v_known) {
         constexpr int t = decltype(tt)::value;
-        const int st = it & 1, j = j_lo + it;
+        const int st = gk & 1;
         const int jlo = t == 0 ? jlo0 : jlo1;
         if (!v_known) {
-          ok = ready(B_VFULL + st, (it >> 1) & 1, 400 + it);
-          if (ok && j >= j_partial) ok = ready(B_VFIXED, 0, 450);
+          ok = ready(B_VFULL + st, (gk >> 1) & 1, 400);
+          if (ok && j >= j_partial) ok = ready(B_VFIXED, n_fixed & 1, 450);
         }
-        MVB_PTRACE(1, it, 6);
         const uint64_t vd = v_desc0 + ((st * C::KV_BYTES) >> 4);
-        const uint32_t first = (j == jlo) ? 0u : 1u;
+        uint32_t first = 1u;
+        if (j == jlo) {
+          first = 0u;
+          if (ok && n_act[t] > 0) ok = ready(B_OFREE + t, (n_act[t] - 1) & 1, 460);
+        }
 #pragma unroll
         for (int h = 0; h < BN / 64; ++h) {
-          if (ok) ok = ready(B_PFULL + 2 * t + h, (j - jlo) & 1, 500 + it);
+          if (ok) ok = ready(B_PFULL + 2 * t + h, n_pv[t] & 1, 500);
           if (!ok) return;
           tc_fence_after();
-          MVB_PTRACE(1, it, 7);
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             const int ks = h * 4 + k4;
             umma_bf16_ts(tmem + C::O_COL + t * D, tmem + C::S_COL + t * BN + ks * 8, vd + ((ks * 2048) >> 4), IDESC_O,
                          ks > 0 ? 1u : first);
           }
-          MVB_PTRACE(1, it, (t == 0 ? 5 : 3));
         }
-        umma_commit(&bars[B_ODONE + t]);
+        if (j == (t == 0 ? jhi0 : jhi1)) umma_commit(&bars[B_ODONE + t]);   // the item's last product: the epilogue waits for it
+        ++n_pv[t];
       };
       using T0 = std::integral_constant<int, 0>;
       using T1 = std::integral_constant<int, NQ - 1>;
-      bool prev_a0 = false, prev_a1 = false;                  // was tile 0 / tile NQ-1 active in the previous step
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int st = it & 1, j = j_lo + it;
-        MVB_PTRACE(1, it, 0);
-        ok = ready(B_KFULL + st, (it >> 1) & 1, 600 + it);
-        if (!ok) break;
-        tc_fence_after();
-        MVB_PTRACE(1, it, 1);
-        const bool a0 = j >= jlo0 && j <= jhi0;
-        // interleave the tiles: S0(j), PV1(j-1), S1(j), PV0(j)
-        if (a0) {
-          if (j == jlo0) ok = ready(B_QFULL + 0, 0, 610);
-          if (ok) issue_s(T0{}, st);
+      Item item;
+      for (uint32_t n_item = 0; ok && next_item(n_item, item); ++n_item) {
+        jlo0 = item.jlo[0]; jhi0 = item.jhi[0];
+        jlo1 = item.jlo[NQ - 1]; jhi1 = item.jhi[NQ - 1];     // tile NQ-1 (== tile 0 when NQ == 1)
+        j_lo = item.j_lo;
+        j_partial = item.k_len / BN;                          // first KV tile with rows past the end
+        const int n_it = item.n_it;
+        const bool rows1 = item.rows[NQ - 1] > 0;
+        bool prev_a0 = false, prev_a1 = false;                // was tile 0 / tile NQ-1 active in the previous step
+        for (int it = 0; it < n_it && ok; ++it, ++g) {
+          const int st = g & 1, j = j_lo + it;
+          ok = ready(B_KFULL + st, (g >> 1) & 1, 600);
+          if (!ok) break;
+          tc_fence_after();
+          const bool a0 = j >= jlo0 && j <= jhi0;
+          // interleave the tiles: S0(j), PV1(j-1), S1(j), PV0(j)
+          if (a0) {
+            if (j == jlo0) ok = ready(B_QFULL + 0, n_act[0] & 1, 610);
+            if (ok) issue_s(T0{}, st);
+          }
+          if constexpr (NQ > 1) {
+            if (it >= 1 && ok) {
+              if (prev_a1) pv_step(T1{}, g - 1, j - 1, prev_a0);   // tile 0's PV already waited for that V tile
+              if (ok) umma_commit(&bars[B_VFREE + ((g - 1) & 1)]);
+            }
+            const bool a1 = rows1 && j >= jlo1 && j <= jhi1;
+            if (ok && a1) {
+              if (j == jlo1) ok = ready(B_QFULL + NQ - 1, n_act[NQ - 1] & 1, 611);
+              if (ok) issue_s(T1{}, st);
+            }
+            prev_a1 = a1;
+          }
+          if (ok) {
+            umma_commit(&bars[B_KFREE + st]);
+            if (it == n_it - 1) umma_commit(&bars[B_QFREE]);  // the item's last S product has been issued
+          }
+          if (ok && a0) pv_step(T0{}, g, j, false);
+          if (NQ == 1 && ok) umma_commit(&bars[B_VFREE + st]);
+          prev_a0 = a0;
         }
-        MVB_PTRACE(1, it, 2);
         if constexpr (NQ > 1) {
-          if (it >= 1 && ok) {
-            if (prev_a1) pv_step(T1{}, it - 1, prev_a0);      // tile 0's PV already waited for that V tile
-            if (ok) umma_commit(&bars[B_VFREE + ((it - 1) & 1)]);
+          if (ok) {
+            if (prev_a1) pv_step(T1{}, g - 1, j_lo + n_it - 1, prev_a0);
+            if (ok) umma_commit(&bars[B_VFREE + ((g - 1) & 1)]);
           }
-          MVB_PTRACE(1, it, 3);
-          const bool a1 = rows_t[NQ - 1] > 0 && j >= jlo1 && j <= jhi1;
-          if (ok && a1) {
-            if (j == jlo1) ok = ready(B_QFULL + NQ - 1, 0, 611);
-            if (ok) issue_s(T1{}, st);
-          }
-          prev_a1 = a1;
         }
-        if (ok) umma_commit(&bars[B_KFREE + st]);
-        MVB_PTRACE(1, it, 4);
-        if (ok && a0) pv_step(T0{}, it, false);
-        MVB_PTRACE(1, it, 5);
-        if (NQ == 1 && ok) umma_commit(&bars[B_VFREE + st]);
-        prev_a0 = a0;
+        if (item.j_hi >= j_partial) ++n_fixed;
+        ++n_act[0];
+        if (NQ > 1 && rows1) ++n_act[NQ - 1];
       }
-      if constexpr (NQ > 1) {
-        if (ok) {
-          if (prev_a1) pv_step(T1{}, n_it - 1, prev_a0);
-          if (ok) umma_commit(&bars[B_VFREE + ((n_it - 1) & 1)]);
-        }
-      }
-      MVB_PT_FLUSH(1);
     }
     __syncwarp();
   } else {
     // ============================ softmax warpgroup of query tile t ==================================
     const int t = warp >> 2;
     const int row = tid & 127;                                // row of the tile = TMEM lane
-    if (rows_t[t] > 0) {
-      const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-      const uint32_t s_addr = lane_addr + C::S_COL + t * BN;
-      const uint32_t o_addr = lane_addr + C::O_COL + t * D;
-      const int my_pos = pf_t[t] + row;                       // absolute position of this row's query
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t s_addr = lane_addr + C::S_COL + t * BN;
+    const uint32_t o_addr = lane_addr + C::O_COL + t * D;
+    uint32_t n_s = 0, n_epi = 0;                              // S tiles consumed (S / P parity), epilogues done (O parity)
+    bool ok = true;
+    Item item;
+    MVB_EV_DECL(2 + t, row == 0)
+    MVB_EV(30);
+    for (uint32_t n_item = 0; ok && next_item(n_item, item); ++n_item) {
+      MVB_EV(31);
+      // this group's tile, picked with selects so the item stays in registers
+      int rows_me = item.rows[0], pf_me = item.pf[0], pl_me = item.pl[0], jlo_me = item.jlo[0], jhi_me = item.jhi[0],
+          roff_me = item.roff[0], head_me = item.head[0];
+#pragma unroll
+      for (int u = 1; u < NQ; ++u)
+        if (t == u) {
+          rows_me = item.rows[u]; pf_me = item.pf[u]; pl_me = item.pl[u]; jlo_me = item.jlo[u]; jhi_me = item.jhi[u];
+          roff_me = item.roff[u]; head_me = item.head[u];
+        }
+      if (rows_me <= 0) continue;
+      const int my_pos = pf_me + row;                    // absolute position of this row's query
       const int hi_key = my_pos;
       const int lo_key = p.window_left >= 0 ? my_pos - p.window_left : 0;
       float m_run = -INFINITY, l_run = 0.f;
-      bool ok = true;
-      MVB_PT_DECL
-      const int n_itt = jhi_t[t] - jlo_t[t] + 1;
-      for (int itt = 0; itt < n_itt && ok; ++itt) {
-        const int j = jlo_t[t] + itt, col0 = j * BN;
-        if (row == 0) MVB_PTRACE(2 + t, itt, 0);
-        ok = wait(B_SFULL + t, itt & 1, 700 + itt);
+      const int n_itt = jhi_me - jlo_me + 1;
+      for (int itt = 0; itt < n_itt && ok; ++itt, ++n_s) {
+        const int j = jlo_me + itt, col0 = j * BN;
+        ok = wait(B_SFULL + t, n_s & 1, 700);
         if (!ok) break;
         tc_fence_after();
-        if (row == 0) MVB_PTRACE(2 + t, itt, 1);
-        const bool need_mask = (col0 + BN - 1 > pf_t[t]) || (p.window_left >= 0 && col0 < pl_t[t] - p.window_left);
-        // visible keys of this row inside the tile: [vis_lo, vis_hi] relative to col0 (only used when masking)
-        const int vis_lo = lo_key - col0, vis_hi = hi_key - col0;
-        // pass 1: row maximum (two code paths so the common unmasked tile carries no mask arithmetic)
-        float tile_max = -INFINITY;
+        MVB_EV(32);
+        // Visible keys of this row inside the tile: [vis_lo, vis_hi] relative to col0.  The rows of a
+        // warp are consecutive, so a 32-key chunk is classified once per warp: visible to all 32 rows
+        // (no mask arithmetic), to none (not loaded at all; P = 0), or mixed (per-element mask bits).
+        const int vis_hi = hi_key - col0;
+        const int vis_lo = p.window_left >= 0 ? lo_key - col0 : -0x40000000;
+        const int w_hi = vis_hi - lane, w_lo = vis_lo - lane;     // bounds of the warp's first row; its last row: + 31
+        auto chunk_class = [&](int cb) -> int {
+          if (cb + 31 <= w_hi && cb >= w_lo + 31) return 0;
+          if (cb > w_hi + 31 || cb + 31 < w_lo) return 2;
+          return 1;
+        };
+        auto visible_bits = [&](int cb) -> uint32_t {             // bit i: key cb + i is visible to this row
+          const int lo = max(vis_lo - cb, 0), hi = min(vis_hi - cb, 31);
+          return hi < lo ? 0u : ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo));
+        };
+        // Two bodies.  Tiles that every row of the warp sees completely (the common case) bring the
+        // thread's whole row of S into registers once - one wait for all the loads, so their latency is
+        // paid once per tile - and keep it there for both passes, with no mask code at all.  The other
+        // tiles (the diagonal, the window's edge) go chunk by chunk and read S twice.
+        float sum0 = 0.f, sum1 = 0.f, alpha = 1.f, m_use = m_run;
+        constexpr int NCH = BN / 32;
+        // new running maximum (lazy: keep the old one unless the tile's is more than 2^8 larger) and the
+        // rescale of O that goes with it; S_t(itt) complete implies PV_t(itt-1) complete (one thread
+        // issues both, in order), so O is ours
+        auto new_max = [&](float tile_max) {
+          tile_max *= p.scale_log2;                           // scale > 0, so max commutes with it
+          if (tile_max > m_run + 8.f || (m_run == -INFINITY && tile_max > -INFINITY)) {
+            m_use = tile_max;
+            alpha = fast_exp2(m_run - m_use);                 // m_run = -inf -> 0
+          }
+          if (itt > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+            for (int c = 0; c < D / 16; ++c) {                // rare: small chunks, to stay short of registers
+              uint32_t r[16];
+              tmem_ld_32x16(o_addr + c * 16, r);
+              tmem_wait_ld();
 #pragma unroll
-        for (int hf = 0; hf < BN / 64; ++hf) {
-          uint32_t r0[32], r1[32];
-          tmem_ld_32x32(s_addr + hf * 64, r0);
-          tmem_ld_32x32(s_addr + hf * 64 + 32, r1);
-          tmem_wait_ld();
-          if (!need_mask) {
-            float m0 = -INFINITY, m1 = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              m0 = fmaxf(m0, __uint_as_float(r0[i]));
-              m1 = fmaxf(m1, __uint_as_float(r1[i]));
-            }
-            tile_max = fmaxf(tile_max, fmaxf(m0, m1));
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int c0 = hf * 64 + i, c1 = c0 + 32;
-              const float x0 = (c0 >= vis_lo && c0 <= vis_hi) ? __uint_as_float(r0[i]) : -INFINITY;
-              const float x1 = (c1 >= vis_lo && c1 <= vis_hi) ? __uint_as_float(r1[i]) : -INFINITY;
-              tile_max = fmaxf(tile_max, fmaxf(x0, x1));
+              for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x16(o_addr + c * 16, r);
             }
           }
-        }
-        if (row == 0) MVB_PTRACE(2 + t, itt, 2);
-        tile_max *= p.scale_log2;                             // scale > 0, so max commutes with it
-        // lazy rescale: keep the old max unless the new one is more than 2^8 larger
-        float m_use = m_run, alpha = 1.f;
-        if (tile_max > m_run + 8.f || (m_run == -INFINITY && tile_max > -INFINITY)) {
-          m_use = tile_max;
-          alpha = fast_exp2(m_run - m_use);                   // m_run = -inf -> 0
-        }
-        const float m_safe = m_use == -INFINITY ? 0.f : m_use;
-        // S_t(itt) complete implies PV_t(itt-1) complete (one thread issues both, in order), so O is ours
-        if (itt > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(o_addr + c * 32, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(o_addr + c * 32, r);
-          }
-        }
-        if (row == 0) MVB_PTRACE(2 + t, itt, 3);
-        // pass 2: P = exp2(S * scale - m) as packed bf16 over the first BN/2 columns of S, published per half
-        float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-        for (int hf = 0; hf < BN / 64; ++hf) {
-          uint32_t r0[32], r1[32], pk[32];
-          tmem_ld_32x32(s_addr + hf * 64, r0);
-          tmem_ld_32x32(s_addr + hf * 64 + 32, r1);
-          tmem_wait_ld();
-          if (!need_mask) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float e0 = fast_exp2(fmaf(__uint_as_float(r0[i]), p.scale_log2, -m_safe));
-              const float e1 = fast_exp2(fmaf(__uint_as_float(r0[i + 1]), p.scale_log2, -m_safe));
-              const float f0 = fast_exp2(fmaf(__uint_as_float(r1[i]), p.scale_log2, -m_safe));
-              const float f1 = fast_exp2(fmaf(__uint_as_float(r1[i + 1]), p.scale_log2, -m_safe));
-              sum0 += e0 + e1; sum1 += f0 + f1;
-              pk[i >> 1] = pack_bf16(e0, e1);                 // keys hf*64 + i, i+1      -> word (hf*64 + i)/2
-              pk[16 + (i >> 1)] = pack_bf16(f0, f1);          // keys hf*64 + 32 + i, ... -> word 16 + ...
+        };
+        // P = exp2(S * scale - m) as packed bf16 over the first BN/2 columns of S (keys c*32 + i, i+1 ->
+        // word c*16 + i/2), written per 32 keys and published per 64 by one lane per warp
+        auto publish_p = [&](int c, const uint32_t (&pk)[16]) {
+          tmem_st_32x16(s_addr + c * 16, pk);
+          if (c & 1) {
+            tmem_wait_st();                                   // warp-wide: every lane's words are in tensor memory
+            if (lane == 0) {
+              tc_fence_before();
+              mbar_arrive(&bars[B_PFULL + 2 * t + (c >> 1)]);
             }
-          } else {
+          }
+        };
+        if (w_hi >= BN - 1 && w_lo + 31 <= 0) {
+          uint32_t sreg[NCH][32];
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) tmem_ld_32x32(s_addr + c * 32, sreg[c]);
+          tmem_wait_ld();
+          MVB_EV(36);
+          float max0 = -INFINITY, max1 = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              max0 = fmax3(max0, __uint_as_float(sreg[c][i]), __uint_as_float(sreg[c][i + 1]));
+              max1 = fmax3(max1, __uint_as_float(sreg[c][i + 2]), __uint_as_float(sreg[c][i + 3]));
+            }
+          MVB_EV(37);
+          new_max(fmaxf(max0, max1));
+          const float m_safe = m_use == -INFINITY ? 0.f : m_use;
+          MVB_EV(38);
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            uint32_t pk[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const int c0 = hf * 64 + i, c1 = c0 + 32;
-              const float a0 = (c0 >= vis_lo && c0 <= vis_hi) ? __uint_as_float(r0[i]) : -INFINITY;
-              const float a1 = (c0 + 1 >= vis_lo && c0 + 1 <= vis_hi) ? __uint_as_float(r0[i + 1]) : -INFINITY;
-              const float b0 = (c1 >= vis_lo && c1 <= vis_hi) ? __uint_as_float(r1[i]) : -INFINITY;
-              const float b1 = (c1 + 1 >= vis_lo && c1 + 1 <= vis_hi) ? __uint_as_float(r1[i + 1]) : -INFINITY;
-              const float e0 = fast_exp2(fmaf(a0, p.scale_log2, -m_safe)), e1 = fast_exp2(fmaf(a1, p.scale_log2, -m_safe));
-              const float f0 = fast_exp2(fmaf(b0, p.scale_log2, -m_safe)), f1 = fast_exp2(fmaf(b1, p.scale_log2, -m_safe));
-              sum0 += e0 + e1; sum1 += f0 + f1;
+              const float e0 = fast_exp2(fmaf(__uint_as_float(sreg[c][i]), p.scale_log2, -m_safe));
+              const float e1 = fast_exp2(fmaf(__uint_as_float(sreg[c][i + 1]), p.scale_log2, -m_safe));
+              sum0 += e0; sum1 += e1;
               pk[i >> 1] = pack_bf16(e0, e1);
-              pk[16 + (i >> 1)] = pack_bf16(f0, f1);
+            }
+            publish_p(c, pk);
+            if (c == 1) MVB_EV(39);
+          }
+        } else {
+          // chunks every row of the warp sees completely run the plain code here too
+          float tile_max = -INFINITY;
+#pragma unroll 1
+          for (int c = 0; c < NCH; ++c) {
+            const int cl = chunk_class(c * 32);
+            if (cl == 2) continue;
+            uint32_t r[32];
+            tmem_ld_32x32(s_addr + c * 32, r);
+            tmem_wait_ld();
+            if (cl == 0) {
+              float max0 = -INFINITY, max1 = -INFINITY;
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                max0 = fmax3(max0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                max1 = fmax3(max1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+              }
+              tile_max = fmax3(tile_max, max0, max1);
+            } else {
+              const uint32_t bits = visible_bits(c * 32);
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                tile_max = fmaxf(tile_max, (bits >> i) & 1u ? __uint_as_float(r[i]) : -INFINITY);
             }
           }
-          tmem_st_32x32(s_addr + hf * 32, pk);
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(&bars[B_PFULL + 2 * t + hf]);
+          new_max(tile_max);
+          const float m_safe = m_use == -INFINITY ? 0.f : m_use;
+#pragma unroll 1
+          for (int c = 0; c < NCH; ++c) {
+            uint32_t pk[16];
+            const int cl = chunk_class(c * 32);
+            if (cl == 2) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pk[i] = 0u;
+            } else {
+              uint32_t r[32];
+              tmem_ld_32x32(s_addr + c * 32, r);
+              tmem_wait_ld();
+              if (cl == 1) {
+                const uint32_t bits = visible_bits(c * 32);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (!((bits >> i) & 1u)) r[i] = 0xff800000u;  // -inf
+              }
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float e0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_safe));
+                const float e1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_safe));
+                sum0 += e0; sum1 += e1;
+                pk[i >> 1] = pack_bf16(e0, e1);
+              }
+            }
+            publish_p(c, pk);
+          }
         }
         l_run = l_run * alpha + (sum0 + sum1);
         m_run = m_use;
-        if (row == 0) MVB_PTRACE(2 + t, itt, 4);
+        MVB_EV(33);
       }
-      if (row == 0) { MVB_PT_FLUSH(2 + t); }
-      // ---- epilogue ---------------------------------------------------------------------------------
-      if (ok) ok = wait(B_ODONE + t, (n_itt - 1) & 1, 800);
+      // ---- epilogue: while it runs, the other roles are already at work on the next item ------------
+      if (ok) ok = wait(B_ODONE + t, n_epi & 1, 800);
+      ++n_epi;
+      MVB_EV(34);
       if (ok) {
         tc_fence_after();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* orow = p.out + (static_cast<int64_t>(q0) + row0 + roff_t[t] + row) * p.out_stride +
-                              static_cast<int64_t>(head_t[t]) * D;
+        // the whole row of O, normalised, as bf16 pairs in registers; then O_t belongs to the next item
+        uint32_t packed[D / 2];
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(o_addr + c * 32, r);
           tmem_wait_ld();
-          if (row < rows_t[t]) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 w;
-              w.x = pack_bf16(__uint_as_float(r[8 * q + 0]) * inv, __uint_as_float(r[8 * q + 1]) * inv);
-              w.y = pack_bf16(__uint_as_float(r[8 * q + 2]) * inv, __uint_as_float(r[8 * q + 3]) * inv);
-              w.z = pack_bf16(__uint_as_float(r[8 * q + 4]) * inv, __uint_as_float(r[8 * q + 5]) * inv);
-              w.w = pack_bf16(__uint_as_float(r[8 * q + 6]) * inv, __uint_as_float(r[8 * q + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = w;
-            }
-          }
+          for (int i = 0; i < 16; ++i)
+            packed[c * 16 + i] = pack_bf16(__uint_as_float(r[2 * i]) * inv, __uint_as_float(r[2 * i + 1]) * inv);
         }
+        if (lane == 0) {                                      // the wait above is warp-wide
+          tc_fence_before();
+          mbar_arrive(&bars[B_OFREE + t]);
+        }
+        MVB_EV(35);
+        // A thread owns a row, so storing from registers would touch 32 lines per instruction.  Each
+        // warp turns its 32 rows through a 4 KB staging tile (16-byte units XOR-swizzled by the row,
+        // conflict-free both ways) and writes whole 128-byte lines, 64 columns at a time.
+        const uint32_t stage = stage_s + warp * 4096;
+        const int wrow0 = (warp & 3) * 32;
+        __nv_bfloat16* obase = p.out + (static_cast<int64_t>(item.q0) + item.row0 + roff_me + wrow0) * p.out_stride +
+                               static_cast<int64_t>(head_me) * D;
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 128 + ((u ^ (lane & 7)) << 4)),
+                         "r"(packed[h * 32 + u * 4]), "r"(packed[h * 32 + u * 4 + 1]), "r"(packed[h * 32 + u * 4 + 2]),
+                         "r"(packed[h * 32 + u * 4 + 3]) : "memory");
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3), un = lane & 7;
+            uint4 w;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                         : "r"(stage + rr * 128 + ((un ^ (rr & 7)) << 4)) : "memory");
+            if (wrow0 + rr < rows_me)
+              *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(rr) * p.out_stride + h * 64 + un * 8) = w;
+          }
+          __syncwarp();
+        }
+        MVB_EV(36);
       }
     }
   }
@@ -526,10 +746,10 @@ static int launch_prefill(const PrefillOperands& op, const PrefillParams& p, int
 
 }  // namespace mvb
 
-#ifdef MVB_PREFILL_TRACE
-extern "C" int mvb_debug_set_prefill_trace(void* ptr) {
+#ifdef MVB_PREFILL_EVLOG
+extern "C" int mvb_debug_set_prefill_evlog(void* ptr) {
   unsigned long long* p = static_cast<unsigned long long*>(ptr);
-  return cudaMemcpyToSymbol(mvb::g_prefill_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -1;
+  return cudaMemcpyToSymbol(mvb::g_prefill_evlog, &p, sizeof(p)) == cudaSuccess ? 0 : -1;
 }
 #endif
 
