@@ -271,9 +271,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         }
       }
       if (!item.empty) {
-        if (lane == 0 && ok) {
-          // the Q tiles are single-buffered: every S product of the previous item must have read them
-          if (n_pub >= 1) ok = wait(B_QFREE, (n_pub - 1) & 1, 920);
+        // The Q tiles are single-buffered: every S product of the previous item must have read them.
+        // They are asked for after the item's first K and V tiles, which do not have to wait for that.
+        auto load_q = [&]() {                                 // lane 0
+          if (n_pub >= 2) ok = wait(B_QFREE, n_pub & 1, 920);
           MVB_EV(13);
 #pragma unroll
           for (int t = 0; t < NQ; ++t) {
@@ -288,7 +289,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                     "r"(item.q0 + item.row0 + item.roff[t]) : "memory");
             }
           }
-        }
+        };
         ++n_pub;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         for (int it = 0; it < item.n_it && ok; ++it, ++g) {
@@ -302,6 +303,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             if (ok && g >= 2) ok = wait(B_VFREE + st, ring_parity ^ 1, 200);
             if (ok) { load_tile(&v_map, v_s + st * C::KV_BYTES, &bars[B_VFULL + st], z); ++v_issued; }
             MVB_EV(16);
+            if (ok && it == 0) load_q();
           }
           ok = __shfl_sync(0xffffffffu, ok, 0);
           const int valid = item.k_len - j * BN;
@@ -428,22 +430,29 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         const int n_it = item.n_it;
         const bool rows1 = item.rows[NQ - 1] > 0;
         bool prev_a0 = false, prev_a1 = false;                // was tile 0 / tile NQ-1 active in the previous step
-        for (int it = 0; it < n_it && ok; ++it, ++g) {
+        // With two tiles the loop takes one extra step for the last P_1 V, so that the tail runs the
+        // loop's own (warm) code.
+        for (int it = 0; it < n_it + (NQ > 1 ? 1 : 0) && ok; ++it, ++g) {
           const int st = g & 1, j = j_lo + it;
-          ok = ready(B_KFULL + st, (g >> 1) & 1, 600);
-          if (!ok) break;
-          tc_fence_after();
-          const bool a0 = j >= jlo0 && j <= jhi0;
-          // interleave the tiles: S0(j), PV1(j-1), S1(j), PV0(j)
-          if (a0) {
-            if (j == jlo0) ok = ready(B_QFULL + 0, n_act[0] & 1, 610);
-            if (ok) issue_s(T0{}, st);
+          const bool body = it < n_it;
+          bool a0 = false;
+          if (body) {
+            ok = ready(B_KFULL + st, (g >> 1) & 1, 600);
+            if (!ok) break;
+            tc_fence_after();
+            a0 = j >= jlo0 && j <= jhi0;
+            // interleave the tiles: S0(j), PV1(j-1), S1(j), PV0(j)
+            if (a0) {
+              if (j == jlo0) ok = ready(B_QFULL + 0, n_act[0] & 1, 610);
+              if (ok) issue_s(T0{}, st);
+            }
           }
           if constexpr (NQ > 1) {
             if (it >= 1 && ok) {
               if (prev_a1) pv_step(T1{}, g - 1, j - 1, prev_a0);   // tile 0's PV already waited for that V tile
               if (ok) umma_commit(&bars[B_VFREE + ((g - 1) & 1)]);
             }
+            if (!body) break;                                 // (leaves g on the next ring position)
             const bool a1 = rows1 && j >= jlo1 && j <= jhi1;
             if (ok && a1) {
               if (j == jlo1) ok = ready(B_QFULL + NQ - 1, n_act[NQ - 1] & 1, 611);
@@ -458,12 +467,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           if (ok && a0) pv_step(T0{}, g, j, false);
           if (NQ == 1 && ok) umma_commit(&bars[B_VFREE + st]);
           prev_a0 = a0;
-        }
-        if constexpr (NQ > 1) {
-          if (ok) {
-            if (prev_a1) pv_step(T1{}, g - 1, j_lo + n_it - 1, prev_a0);
-            if (ok) umma_commit(&bars[B_VFREE + ((g - 1) & 1)]);
-          }
         }
         if (item.j_hi >= j_partial) ++n_fixed;
         ++n_act[0];
