@@ -73,8 +73,8 @@ struct PrefillParams {
 // P is published in 64-key halves (slot B_PFULL + 2 * tile + half) so the PV product of the first
 // half starts while the second half is still being exponentiated.
 enum : int { B_QFULL = 0, B_KFULL = 2, B_VFULL = 4, B_KFREE = 6, B_VFREE = 8, B_SFULL = 10, B_PFULL = 12,
-             B_ODONE = 16, B_OFREE = 18, B_VFIXED = 20, B_QFREE = 21, B_ITEM_FULL = 22, B_ITEM_FREE = 24,
-             B_CLC = 26, B_COUNT = 27 };
+             B_ODONE = 16, B_OFREE = 18, B_VFIXED = 20, B_QFREE = 22, B_ITEM_FULL = 23, B_ITEM_FREE = 25,
+             B_CLC = 27, B_COUNT = 28 };
 
 template <int D, int BN, int NQ>
 struct PrefillCfg {
@@ -86,7 +86,7 @@ struct PrefillCfg {
   // after the tiles: barriers, the tensor-memory address, the failure flag, two item slots and the
   // launch-control response
   static constexpr int CTRL_BYTES = 512;
-  static constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_FAIL = OFF_TMEM_SLOT + 4, OFF_ITEMS = 224, OFF_CLC = 256;
+  static constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_FAIL = OFF_TMEM_SLOT + 4, OFF_ITEMS = 240, OFF_CLC = 272;
   static constexpr int STAGE_BYTES = NQ * 4 * 4096;     // a 32-row x 128-byte output staging tile per softmax warp
   static constexpr int SMEM = NQ * Q_BYTES + 4 * KV_BYTES + 1024 /*align*/ + CTRL_BYTES + STAGE_BYTES;
   static constexpr int TMEM_COLS = NQ * (BN + D) <= 256 ? 256 : 512;   // power of two
@@ -320,7 +320,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
               }
               fence_proxy_async();
               __syncwarp();
-              if (lane == 0) mbar_arrive(&bars[B_VFIXED]);
+              if (lane == 0) mbar_arrive(&bars[B_VFIXED + st]);
             }
           }
         }
@@ -371,7 +371,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       uint32_t g = 0;                                         // KV tiles consumed (ring position)
       uint32_t n_pv[2] = {0, 0};                              // PV products issued per query tile (P parity)
       uint32_t n_act[2] = {0, 0};                             // items in which the query tile had rows (Q / O parity)
-      uint32_t n_fixed = 0;                                   // partial V tiles seen
+      uint32_t fix_parity = 0;                                // bit st: parity of the next V fix-up on ring stage st
       int jlo0 = 0, jhi0 = -1, jlo1 = 0, jhi1 = -1, j_lo = 0, j_partial = 0;
       auto ready = [&](int slot, uint32_t parity, int where) -> bool {
         return mbar_try_wait(&bars[slot], parity) ? true : wait(slot, parity, where);
@@ -396,7 +396,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         const int jlo = t == 0 ? jlo0 : jlo1;
         if (!v_known) {
           ok = ready(B_VFULL + st, (gk >> 1) & 1, 400);
-          if (ok && j >= j_partial) ok = ready(B_VFIXED, n_fixed & 1, 450);
+          if (ok && j >= j_partial) ok = ready(B_VFIXED + st, (fix_parity >> st) & 1, 450);
         }
         const uint64_t vd = v_desc0 + ((st * C::KV_BYTES) >> 4);
         uint32_t first = 1u;
@@ -468,7 +468,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           if (NQ == 1 && ok) umma_commit(&bars[B_VFREE + st]);
           prev_a0 = a0;
         }
-        if (item.j_hi >= j_partial) ++n_fixed;
+        // a partial tile is an item's last one: its fix-up, on the ring stage just left, has been consumed
+        if (item.j_hi >= j_partial) fix_parity ^= 1u << ((g - 1) & 1);
         ++n_act[0];
         if (NQ > 1 && rows1) ++n_act[NQ - 1];
       }

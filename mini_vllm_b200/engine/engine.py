@@ -110,6 +110,7 @@ class Engine:
         reqs = [self.submit(prompt, sp) for prompt, sp in zip(prompts, sampling_params)]
         if not use_tqdm and self._schedule_is_token_independent(sampling_params):
             self._generate_pipelined(reqs)
+            self.executor.check_device_status()    # every result is on the host by now: the read costs no extra sync
             dec = self.tokenizer.decode if self.tokenizer is not None else (lambda toks: None)
             return [{"prompt": dec(r.prompt_tokens), "completion": dec(r.completion_tokens),
                      "tokens": r.completion_tokens} for r in sorted(reqs, key=lambda r: r.id)]
@@ -131,6 +132,7 @@ class Engine:
                 shown = len(done)
         if pbar is not None:
             pbar.close()
+        self.executor.check_device_status()        # a kernel that skipped a bad access or gave up a wait says so here
         done.sort(key=lambda r: r.id)
         dec = self.tokenizer.decode if self.tokenizer is not None else (lambda toks: None)
         return [{"prompt": dec(r.prompt_tokens), "completion": dec(r.completion_tokens),

@@ -112,3 +112,16 @@ def test_config3_prefill_part(cuda):
     q_lens = [n - c for n, c in zip(case.prefill_lens, case.prefill_cached)]
     run_paged(cuda, q_lens, case.prefill_lens, 16, 8, 128, tables=case.prefill_blocks,
               num_blocks=case.pool_blocks, g=g)
+
+
+def test_many_short_sequences_between_long_ones(cuda):
+    """A prefill step as the scheduler packs it: a few long prompts among dozens of one-tile ones, each
+    ending in a partial KV tile.  One CTA then works through many items back to back, and the producer
+    fixes up the partial V tile of the next items while the current one is still being multiplied; run
+    a few times because the interleaving is timing dependent."""
+    g = generator(11)
+    lens = [2440, 37, 54, 101, 2089, 33, 77, 130, 65, 1500] + [int(x) for x in torch.randint(32, 200, (40,), generator=g)]
+    for rep in range(3):
+        run_dense(cuda, lens, 16, 8, 128, seed=20 + rep, packed_qkv=True)
+    k_lens = lens[:24]
+    run_paged(cuda, k_lens, k_lens, 16, 8, 128, seed=30)
