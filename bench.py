@@ -99,18 +99,20 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------------
+def build_config(workload: str = "config5") -> Config:
+    if workload == "config5":        # long prompts, hundreds of live sequences: a large pool, preemption allowed
+        # up to 512 live sequences (the reference's default max_num_batched_seqs), all decode batches from graphs
+        return Config(hf_config=qwen3_shape(), kv_cache_num_blocks=4096,
+                      max_num_batched_seqs=512, max_graph_batch_size=512,
+                      max_num_batched_tokens=16384, gpu_memory_utilization=0.85, use_cuda_graph=True, seed=0)
+    return Config(hf_config=qwen3_shape(), kv_cache_num_blocks=512, max_num_batched_seqs=64,
+                  max_num_batched_tokens=16384, gpu_memory_utilization=0.5, use_cuda_graph=True, seed=0)
+
+
 def build_engine(local_rank: int, workload: str = "config5"):
     from mini_vllm_b200.engine.engine import Engine
     torch.cuda.set_device(local_rank)
-    if workload == "config5":        # long prompts, hundreds of live sequences: a large pool, preemption allowed
-        # up to 512 live sequences (the reference's default max_num_batched_seqs), all decode batches from graphs
-        cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=4096,
-                     max_num_batched_seqs=512, max_graph_batch_size=512,
-                     max_num_batched_tokens=16384, gpu_memory_utilization=0.85, use_cuda_graph=True, seed=0)
-    else:
-        cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=512, max_num_batched_seqs=64,
-                     max_num_batched_tokens=16384, gpu_memory_utilization=0.5, use_cuda_graph=True, seed=0)
-    return Engine(cfg)
+    return Engine(build_config(workload))
 
 
 def run_job(engine, reqs, record_contexts=None):
@@ -367,11 +369,16 @@ def main():
         print(json.dumps(kernel_extras(torch.device("cuda", 0), peaks, nl=1)))
         return
     if args.engine_steps:
+        import dataclasses
         from mini_vllm_b200.engine.engine import Engine
-        cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=512, max_num_batched_seqs=64,
-                     max_num_batched_tokens=16384, gpu_memory_utilization=0.5, use_cuda_graph=False, seed=0)
-        eng = Engine(cfg)
-        for r in config2_requests(0):
+        torch.cuda.set_device(0)
+        eng = Engine(dataclasses.replace(build_config(args.workload), use_cuda_graph=False))   # every kernel its own launch
+        if args.workload == "config5":
+            from mini_vllm_b200.workloads import config5_requests
+            reqs = config5_requests(seed=0, n=512)
+        else:
+            reqs = config2_requests(0)
+        for r in reqs:
             eng.submit(r.prompt, SamplingParams(max_tokens=r.max_tokens, ignore_eos=True))
         done = 0
         while done < args.engine_steps:
