@@ -331,14 +331,16 @@ def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    vals = []
+    vals, secs = [], []
     for _ in range(max(1, min(args.steps, 3))):
         v, threads, sample, dt = cpu_reference_sample(args.workload)
         vals.append(v)
+        secs.append(dt)
     value = statistics.median(vals)
     line = {"impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(1e3 * statistics.median(secs), 1),      # one step here = the bounded sample
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOADS[args.workload]},
             "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": threads, "kind": "port",
                              "sample": sample},
