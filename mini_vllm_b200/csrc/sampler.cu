@@ -1,5 +1,6 @@
-// Fused temperature / top-k / Gumbel-max sampler: one CTA per logits row (HBM-bound:
-// algorithmic bytes = num_rows * vocab * 2; the top-k passes re-read the row from L2).
+// Fused temperature / top-k / Gumbel-max sampler (HBM-bound: algorithmic bytes = num_rows * vocab * 2):
+// greedy rows are split over a cluster of CTAs, the random path runs one CTA per row and its top-k
+// passes re-read the row from L2.
 //
 // Greedy: argmax of float(logit) / T with the lowest index winning ties, which is what
 // torch.argmax returns on the same fp32 values.
@@ -8,7 +9,10 @@
 // argmax over the kept entries of  logit / T - log(-log(u)),  u from Philox4x32-10 with
 // counter (column/4, row, offset_lo, offset_hi), key (seed_lo, seed_hi), word column%4.
 #include "common.cuh"
+#include "host_util.cuh"
 #include "mini_vllm_b200.h"
+
+#include <cooperative_groups.h>
 
 namespace mvb {
 
@@ -105,20 +109,105 @@ struct SampleParams {
   const int32_t* scatter_index;
 };
 
+// Greedy: a cluster of CTAs per row (1, 2, 4 or 8, chosen on the host so that small batches still fill
+// the GPU), each over a contiguous slice of the vocabulary with 128-bit loads; the slices' winners
+// meet in the first CTA through distributed shared memory.
 __global__ void __launch_bounds__(kSampleThreads) sample_greedy_kernel(const SampleParams p) {
-  const int r = blockIdx.x;
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int parts = static_cast<int>(cluster.num_blocks()), part = static_cast<int>(cluster.block_rank());
+  const int r = blockIdx.x / parts;
+  __shared__ Best slice_best;
   const uint16_t* row = p.logits + r * p.row_stride;
   const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
   const bool scaled = p.temperatures != nullptr;
   const float temp = scaled ? p.temperatures[r] : 1.f;
   Best b{-INFINITY, 0x7fffffff};
-  for_each_logit(row, p.vocab, vec_ok, [&](int c, uint16_t bits) {
+  auto consider = [&](int c, uint16_t bits) {
     float x = bits_to_float(bits);
     if (scaled) x = __fdiv_rn(x, temp);
     if (better(x, c, b.val, b.idx)) { b.val = x; b.idx = c; }
-  });
+  };
+  if (vec_ok) {
+    const int nvec = p.vocab / 8;
+    const int v0 = static_cast<int>(static_cast<int64_t>(nvec) * part / parts);
+    const int v1 = static_cast<int>(static_cast<int64_t>(nvec) * (part + 1) / parts);
+    auto take = [&](int v, const uint4& w) {
+      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        consider(v * 8 + 2 * i, static_cast<uint16_t>(ws[i] & 0xffffu));
+        consider(v * 8 + 2 * i + 1, static_cast<uint16_t>(ws[i] >> 16));
+      }
+    };
+    bool exact_pass = scaled;
+    if (!scaled) {
+      // Unscaled rows are compared as packed bf16 pairs: per 32-bit word of the 128-bit load a running
+      // maximum of each half and the loop count at which that half last grew (strictly, so the first
+      // occurrence stays) - 3 instructions per two logits.  A NaN poisons its running maximum; such a
+      // row is then redone by the exact pass below.
+      __nv_bfloat162 m[4];
+      uint32_t when[4];                                       // two 16-bit loop counts per word, 0xffff = never
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { m[i] = __floats2bfloat162_rn(-INFINITY, -INFINITY); when[i] = 0xffffffffu; }
+      const int vstart = v0 + threadIdx.x;
+      uint32_t count2 = 0;                                    // loop count in both halves
+#pragma unroll 4
+      for (int v = vstart; v < v1; v += kSampleThreads, count2 += 0x00010001u) {
+        const uint4 w = *reinterpret_cast<const uint4*>(row + v * 8);
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&ws[i]);
+          const uint32_t grew = __hgt2_mask(x, m[i]);
+          m[i] = __hmax2_nan(m[i], x);
+          when[i] = (grew & count2) | (~grew & when[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float lo = __low2float(m[i]), hi = __high2float(m[i]);
+        if (lo != lo || hi != hi) exact_pass = true;
+        const uint32_t wl = when[i] & 0xffffu, wh = when[i] >> 16;
+        if (wl != 0xffffu && better(lo, (vstart + static_cast<int>(wl) * kSampleThreads) * 8 + 2 * i, b.val, b.idx)) {
+          b.val = lo; b.idx = (vstart + static_cast<int>(wl) * kSampleThreads) * 8 + 2 * i;
+        }
+        if (wh != 0xffffu && better(hi, (vstart + static_cast<int>(wh) * kSampleThreads) * 8 + 2 * i + 1, b.val, b.idx)) {
+          b.val = hi; b.idx = (vstart + static_cast<int>(wh) * kSampleThreads) * 8 + 2 * i + 1;
+        }
+      }
+      exact_pass = __syncthreads_or(exact_pass);
+      if (exact_pass) { b.val = -INFINITY; b.idx = 0x7fffffff; }
+    }
+    if (exact_pass)
+      for (int v = v0 + threadIdx.x; v < v1; v += kSampleThreads) take(v, *reinterpret_cast<const uint4*>(row + v * 8));
+    if (part == parts - 1)
+      for (int c = nvec * 8 + threadIdx.x; c < p.vocab; c += kSampleThreads) consider(c, row[c]);
+  } else {
+    const int c0 = static_cast<int>(static_cast<int64_t>(p.vocab) * part / parts);
+    const int c1 = static_cast<int>(static_cast<int64_t>(p.vocab) * (part + 1) / parts);
+    for (int c = c0 + threadIdx.x; c < c1; c += kSampleThreads) consider(c, row[c]);
+  }
   b = block_argmax(b);
+  if (parts > 1) {
+    if (threadIdx.x == 0) slice_best = b;
+    cluster.sync();
+    if (part == 0 && threadIdx.x < 32) {
+      Best o{-INFINITY, 0x7fffffff};
+      if (threadIdx.x < parts) o = *cluster.map_shared_rank(&slice_best, threadIdx.x);
+#pragma unroll
+      for (int s = 4; s > 0; s >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, o.val, s);
+        const int oi = __shfl_xor_sync(0xffffffffu, o.idx, s);
+        if (better(ov, oi, o.val, o.idx)) { o.val = ov; o.idx = oi; }
+      }
+      b = o;
+    }
+    cluster.sync();                                          // the slices' shared memory stays alive until it was read
+    if (part != 0) return;
+  }
   if (threadIdx.x == 0) {
+    if (b.idx == 0x7fffffff) b.idx = 0;                       // a row of -inf only: nothing ever exceeded the start value
     p.out[r] = b.idx;
     if (p.scatter_table != nullptr) p.scatter_table[p.scatter_index[r]] = b.idx;
   }
@@ -276,7 +365,21 @@ extern "C" int mvb_sample(const void* logits, int64_t row_stride, int num_rows, 
   SampleParams p{static_cast<const uint16_t*>(logits), row_stride, vocab, temperatures, top_k, top_p, seed, offset,
                  out, scatter_table, scatter_index};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (top_k == nullptr && top_p == nullptr) sample_greedy_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);
-  else sample_topk_gumbel_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);
+  if (top_k == nullptr && top_p == nullptr) {
+    // enough CTAs for two per SM: a cluster of up to 8 per row when the batch is small
+    int parts = 1;
+    while (parts < 8 && static_cast<int64_t>(num_rows) * parts < 2 * sm_count()) parts *= 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(num_rows) * parts);
+    cfg.blockDim = dim3(kSampleThreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = parts; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, sample_greedy_kernel, p) == cudaSuccess ? kOk : kLaunchFailed;
+  }
+  sample_topk_gumbel_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }

@@ -20,6 +20,38 @@ def test_greedy_is_first_argmax(cuda, B, V):
     assert torch.equal(out.cpu(), osamp.greedy(logits))
 
 
+@pytest.mark.parametrize("B", [1, 3, 40, 200, 400])
+def test_greedy_special_values_and_batch_sizes(cuda, B):
+    """The row is split over 1, 2, 4 or 8 CTAs depending on the batch; ties across words of one load,
+    across threads and across slices, signed zeros, -inf rows and NaNs follow torch.argmax."""
+    V = 151936
+    g = generator(100 + B)
+    logits = randn_bf16(g, B, V)
+    top = logits.max().item() + 1.0
+    logits[0, V - 1] = top; logits[0, V // 2 + 3] = top; logits[0, 4097] = top      # same value in three slices
+    if B > 1:
+        logits[1] = float("-inf")                                                  # nothing is larger than the start value
+    if B > 2:
+        logits[2] = -1.0
+        logits[2, 9] = -0.0; logits[2, 8] = 0.0; logits[2, 123456] = 0.0             # +0 == -0: the lowest index wins
+    if B > 3:
+        logits[3, 77777] = float("nan"); logits[3, 99] = top                       # NaN counts as the largest
+        logits[4, 5] = float("-inf"); logits[4, 6] = float("inf"); logits[4, 70000] = float("inf")
+    want = osamp.greedy(logits)
+    if B > 3:
+        assert want[3] == 77777
+    out = ops.sample(logits.to(cuda)).cpu()
+    assert torch.equal(out, want)
+
+
+def test_greedy_unaligned_rows(cuda):
+    """Rows that do not start on 16 bytes take the scalar path."""
+    g = generator(6)
+    full = randn_bf16(g, 9, 5000 + 3)
+    out = ops.sample(full.to(cuda)[:, 3:])
+    assert torch.equal(out.cpu(), osamp.greedy(full[:, 3:]))
+
+
 def test_greedy_with_temperature_and_row_stride(cuda):
     g = generator(5)
     full = randn_bf16(g, 6, 4096 + 8)
