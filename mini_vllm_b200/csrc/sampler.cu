@@ -1,6 +1,6 @@
 // Fused temperature / top-k / Gumbel-max sampler (HBM-bound: algorithmic bytes = num_rows * vocab * 2):
-// greedy rows are split over a cluster of CTAs, the random path runs one CTA per row and its top-k
-// passes re-read the row from L2.
+// greedy rows are split over a cluster of CTAs; the random path runs one CTA per row, reads the row
+// three times (two counting passes and one that moves the kept entries into shared memory).
 //
 // Greedy: argmax of float(logit) / T with the lowest index winning ties, which is what
 // torch.argmax returns on the same fp32 values.
@@ -213,12 +213,20 @@ __global__ void __launch_bounds__(kSampleThreads) sample_greedy_kernel(const Sam
   }
 }
 
+constexpr int kKeptCap = 4096;       // kept (top-k) entries that the random path holds in shared memory
+
 __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(const SampleParams p) {
+  constexpr int NW = kSampleThreads / 32;
+  __shared__ uint32_t hist_w[NW][256];                       // one histogram per warp: no contention between warps
   __shared__ uint32_t hist[256];
   __shared__ float mass[256];
   __shared__ uint32_t sel_s[2];                              // selected bin, entries needed inside it
   __shared__ float self_s[2];                                // nucleus: mass still needed, total mass
+  __shared__ int32_t kept_col[kKeptCap];
+  __shared__ uint16_t kept_bits[kKeptCap];
+  __shared__ uint32_t n_kept_s;
   const int r = blockIdx.x;
+  const int warp = threadIdx.x >> 5;
   const uint16_t* row = p.logits + r * p.row_stride;
   const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
   const float temp = p.temperatures != nullptr ? p.temperatures[r] : 1.f;
@@ -226,13 +234,29 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
   const int k = p.top_k != nullptr ? p.top_k[r] : 0;
   const float top_p = p.top_p != nullptr ? p.top_p[r] : 1.f;
 
+  // counts of one byte of the key over the row (entries for which keep(key) holds), summed into hist
+  auto count_pass = [&](auto bin_of, auto keep) {
+    for (int i = threadIdx.x; i < NW * 256; i += kSampleThreads) (&hist_w[0][0])[i] = 0;
+    __syncthreads();
+    for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) {
+      const uint32_t key = sort_key(bits);
+      if (keep(key)) atomicAdd(&hist_w[warp][bin_of(key)], 1u);
+    });
+    __syncthreads();
+    for (int i = threadIdx.x; i < 256; i += kSampleThreads) {
+      uint32_t n = 0;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) n += hist_w[w][i];
+      hist[i] = n;
+    }
+    __syncthreads();
+  };
+
   uint32_t thresh = 0;                                       // keep keys >= thresh
+  bool compact = false;                                      // the kept entries sit in shared memory
   if (k > 0 && k < p.vocab) {
     // pass 1: high byte
-    for (int i = threadIdx.x; i < 256; i += kSampleThreads) hist[i] = 0;
-    __syncthreads();
-    for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) { atomicAdd(&hist[sort_key(bits) >> 8], 1u); });
-    __syncthreads();
+    count_pass([](uint32_t key) { return key >> 8; }, [](uint32_t) { return true; });
     if (threadIdx.x == 0) {
       uint32_t need = k, bin = 0;
       for (int i = 255; i >= 0; --i) {
@@ -245,13 +269,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
     const uint32_t hi_bin = sel_s[0], need_hi = sel_s[1];
     __syncthreads();
     // pass 2: low byte inside the selected high bin
-    for (int i = threadIdx.x; i < 256; i += kSampleThreads) hist[i] = 0;
-    __syncthreads();
-    for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) {
-      const uint32_t key = sort_key(bits);
-      if ((key >> 8) == hi_bin) atomicAdd(&hist[key & 0xffu], 1u);
-    });
-    __syncthreads();
+    count_pass([](uint32_t key) { return key & 0xffu; }, [&](uint32_t key) { return (key >> 8) == hi_bin; });
     if (threadIdx.x == 0) {
       uint32_t need = need_hi, bin = 0;
       for (int i = 255; i >= 0; --i) {
@@ -259,17 +277,37 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
         need -= hist[i];
       }
       sel_s[0] = bin;
+      n_kept_s = 0;
     }
     __syncthreads();
     thresh = (hi_bin << 8) | sel_s[0];
+    // pass 3: the kept entries (k of them, plus ties at the threshold) move into shared memory; what
+    // follows - maximum, nucleus, the draw - then never goes back to the row
+    for_each_logit(row, p.vocab, vec_ok, [&](int c, uint16_t bits) {
+      if (sort_key(bits) < thresh) return;
+      const uint32_t slot = atomicAdd(&n_kept_s, 1u);
+      if (slot < kKeptCap) { kept_col[slot] = c; kept_bits[slot] = bits; }
+    });
+    __syncthreads();
+    compact = n_kept_s <= kKeptCap;
   }
+  const int n_kept = compact ? static_cast<int>(n_kept_s) : 0;
+  // f(column, bits) for every entry with key >= thresh
+  auto for_each_kept = [&](auto f) {
+    if (compact) {
+      for (int i = threadIdx.x; i < n_kept; i += kSampleThreads) f(kept_col[i], kept_bits[i]);
+    } else {
+      for_each_logit(row, p.vocab, vec_ok, [&](int c, uint16_t bits) {
+        if (sort_key(bits) >= thresh) f(c, bits);
+      });
+    }
+  };
 
   if (top_p < 1.f) {
     // nucleus: the smallest set of the most likely kept tokens whose probability mass reaches top_p,
     // found like the top-k threshold but with histograms of exp(x - max) instead of counts
     Best mx{-INFINITY, 0x7fffffff};
-    for_each_logit(row, p.vocab, vec_ok, [&](int c, uint16_t bits) {
-      if (sort_key(bits) < thresh) return;
+    for_each_kept([&](int c, uint16_t bits) {
       float x = bits_to_float(bits);
       if (scaled) x = __fdiv_rn(x, temp);
       if (better(x, c, mx.val, mx.idx)) { mx.val = x; mx.idx = c; }
@@ -285,10 +323,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
       if (scaled) x = __fdiv_rn(x, temp);
       return expf(x - xmax);
     };
-    for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) {
-      const uint32_t key = sort_key(bits);
-      if (key >= thresh) atomicAdd(&mass[key >> 8], weight(bits));
-    });
+    for_each_kept([&](int, uint16_t bits) { atomicAdd(&mass[sort_key(bits) >> 8], weight(bits)); });
     __syncthreads();
     if (threadIdx.x == 0) {
       float total = 0.f;
@@ -307,9 +342,9 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
     __syncthreads();
     for (int i = threadIdx.x; i < 256; i += kSampleThreads) mass[i] = 0.f;
     __syncthreads();
-    for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) {
+    for_each_kept([&](int, uint16_t bits) {
       const uint32_t key = sort_key(bits);
-      if (key >= thresh && (key >> 8) == hi_bin) atomicAdd(&mass[key & 0xffu], weight(bits));
+      if ((key >> 8) == hi_bin) atomicAdd(&mass[key & 0xffu], weight(bits));
     });
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -332,7 +367,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
   Best b{-INFINITY, 0x7fffffff};
   uint32_t rnd[4];
   int rnd_group = -1;
-  for_each_logit(row, p.vocab, vec_ok, [&](int c, uint16_t bits) {
+  // (the compacted list was made with the top-k threshold; the nucleus may have raised it since)
+  for_each_kept([&](int c, uint16_t bits) {
     if (sort_key(bits) < thresh) return;
     if ((c >> 2) != rnd_group) {
       rnd_group = c >> 2;
