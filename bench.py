@@ -285,6 +285,35 @@ def kernel_extras(dev, peaks, nl=4):
         gbs = byts / ms / 1e6
         out[name] = {"GB/s": round(gbs, 1), "us": round(ms * 1e3, 1), "bytes": byts,
                      "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4)}
+    del gpools
+    # sampler over Qwen3's vocabulary: the 512-row and the 64-row decode batch, greedy and top-k/top-p
+    vocab = 151936
+    for rows in (512, 64):
+        bufs = [torch.randn(rows, vocab, device=dev).to(torch.bfloat16) for _ in range(max(2, min(16, int(600e6 / (rows * vocab * 2)))))]
+        temps = torch.full((rows,), 0.8, device=dev)
+        topk = torch.full((rows,), 50, dtype=torch.int32, device=dev)
+        topp = torch.full((rows,), 0.9, device=dev)
+        for name, call in ((f"sample_greedy_{rows}", lambda x: ops.sample(x)),
+                           (f"sample_top50_p0.9_{rows}", lambda x: ops.sample(x, temps, topk, 1, 0, top_p=topp))):
+            def sweep():
+                for x in bufs:                               # distinct buffers: nothing comes from L2
+                    call(x)
+            sweep()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                sweep()
+            graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / (5 * len(bufs))
+            byts = rows * vocab * 2
+            out[name] = {"GB/s": round(byts / ms / 1e6, 1), "us": round(ms * 1e3, 1), "bytes": byts,
+                         "frac_of_measured_hbm": round(byts / ms / 1e6 / peaks["hbm_gbs"], 4)}
     return out
 
 
