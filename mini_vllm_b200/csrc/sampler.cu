@@ -1,6 +1,6 @@
 // Fused temperature / top-k / Gumbel-max sampler (HBM-bound: algorithmic bytes = num_rows * vocab * 2):
-// greedy rows are split over a cluster of CTAs; the random path runs one CTA per row, reads the row
-// three times (two counting passes and one that moves the kept entries into shared memory).
+// greedy rows are split over a cluster of CTAs; the random path runs one CTA per row and normally
+// reads the row twice (its maximum, then the entries near it into shared memory), else four times.
 //
 // Greedy: argmax of float(logit) / T with the lowest index winning ties, which is what
 // torch.argmax returns on the same fp32 values.
@@ -72,6 +72,28 @@ __device__ __forceinline__ void for_each_logit(const uint16_t* row, int vocab, b
     for (int c = nvec * 8 + threadIdx.x; c < vocab; c += kSampleThreads) f(c, row[c]);
   } else {
     for (int c = threadIdx.x; c < vocab; c += kSampleThreads) f(c, row[c]);
+  }
+}
+
+// Calls f(first column, two packed bf16) for every pair of columns; an odd last column comes with -inf
+// in the upper half (column == vocab: callers that act on columns must check it).
+template <class F>
+__device__ __forceinline__ void for_each_word(const uint16_t* row, int vocab, bool vec_ok, F f) {
+  if (vec_ok) {
+    const int nvec = vocab / 8;
+    for (int v = threadIdx.x; v < nvec; v += kSampleThreads) {
+      const uint4 w = *reinterpret_cast<const uint4*>(row + v * 8);
+      f(v * 8, w.x); f(v * 8 + 2, w.y); f(v * 8 + 4, w.z); f(v * 8 + 6, w.w);
+    }
+    for (int c = nvec * 8 + 2 * threadIdx.x; c < vocab; c += 2 * kSampleThreads) {
+      const uint32_t lo = row[c], hi = c + 1 < vocab ? row[c + 1] : 0xff80u;   // -inf pads an odd tail
+      f(c, lo | (hi << 16));
+    }
+  } else {
+    for (int c = 2 * threadIdx.x; c < vocab; c += 2 * kSampleThreads) {
+      const uint32_t lo = row[c], hi = c + 1 < vocab ? row[c + 1] : 0xff80u;
+      f(c, lo | (hi << 16));
+    }
   }
 }
 
@@ -234,14 +256,21 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
   const int k = p.top_k != nullptr ? p.top_k[r] : 0;
   const float top_p = p.top_p != nullptr ? p.top_p[r] : 1.f;
 
-  // counts of one byte of the key over the row (entries for which keep(key) holds), summed into hist
-  auto count_pass = [&](auto bin_of, auto keep) {
+  // counts of one byte of the key (entries for which keep(key) holds), summed into hist; over the row or,
+  // once the candidates sit in shared memory, over those
+  auto count_pass = [&](bool from_kept, auto bin_of, auto keep) {
     for (int i = threadIdx.x; i < NW * 256; i += kSampleThreads) (&hist_w[0][0])[i] = 0;
     __syncthreads();
-    for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) {
+    auto add = [&](uint16_t bits) {
       const uint32_t key = sort_key(bits);
       if (keep(key)) atomicAdd(&hist_w[warp][bin_of(key)], 1u);
-    });
+    };
+    if (from_kept) {
+      const int n = static_cast<int>(n_kept_s);
+      for (int i = threadIdx.x; i < n; i += kSampleThreads) add(kept_bits[i]);
+    } else {
+      for_each_logit(row, p.vocab, vec_ok, [&](int, uint16_t bits) { add(bits); });
+    }
     __syncthreads();
     for (int i = threadIdx.x; i < 256; i += kSampleThreads) {
       uint32_t n = 0;
@@ -251,12 +280,9 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
     }
     __syncthreads();
   };
-
-  uint32_t thresh = 0;                                       // keep keys >= thresh
-  bool compact = false;                                      // the kept entries sit in shared memory
-  if (k > 0 && k < p.vocab) {
-    // pass 1: high byte
-    count_pass([](uint32_t key) { return key >> 8; }, [](uint32_t) { return true; });
+  // the key of the k-th largest entry by two radix passes (high byte, then low byte inside its bin)
+  auto kth_key = [&](bool from_kept) -> uint32_t {
+    count_pass(from_kept, [](uint32_t key) { return key >> 8; }, [](uint32_t) { return true; });
     if (threadIdx.x == 0) {
       uint32_t need = k, bin = 0;
       for (int i = 255; i >= 0; --i) {
@@ -268,8 +294,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
     __syncthreads();
     const uint32_t hi_bin = sel_s[0], need_hi = sel_s[1];
     __syncthreads();
-    // pass 2: low byte inside the selected high bin
-    count_pass([](uint32_t key) { return key & 0xffu; }, [&](uint32_t key) { return (key >> 8) == hi_bin; });
+    count_pass(from_kept, [](uint32_t key) { return key & 0xffu; }, [&](uint32_t key) { return (key >> 8) == hi_bin; });
     if (threadIdx.x == 0) {
       uint32_t need = need_hi, bin = 0;
       for (int i = 255; i >= 0; --i) {
@@ -277,25 +302,80 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
         need -= hist[i];
       }
       sel_s[0] = bin;
-      n_kept_s = 0;
     }
     __syncthreads();
-    thresh = (hi_bin << 8) | sel_s[0];
-    // pass 3: the kept entries (k of them, plus ties at the threshold) move into shared memory; what
-    // follows - maximum, nucleus, the draw - then never goes back to the row
+    const uint32_t key = (hi_bin << 8) | sel_s[0];
+    __syncthreads();
+    return key;
+  };
+  // entries with key >= lo move into shared memory (all of them counted, the first kKeptCap stored)
+  auto gather = [&](uint32_t lo) {
+    if (threadIdx.x == 0) n_kept_s = 0;
+    __syncthreads();
     for_each_logit(row, p.vocab, vec_ok, [&](int c, uint16_t bits) {
-      if (sort_key(bits) < thresh) return;
+      if (sort_key(bits) < lo) return;
       const uint32_t slot = atomicAdd(&n_kept_s, 1u);
       if (slot < kKeptCap) { kept_col[slot] = c; kept_bits[slot] = bits; }
     });
     __syncthreads();
-    compact = n_kept_s <= kKeptCap;
+  };
+
+  uint32_t thresh = 0;                                       // keep keys >= thresh
+  bool compact = false;                                      // the candidates sit in shared memory
+  if (k > 0 && k < p.vocab) {
+    // First attempt, two reads of the row and hardly an atomic: the largest key, then everything within
+    // one binade below it (128 bf16 steps) into shared memory.  If that holds at least k entries and
+    // fits, the k-th key is found there.
+    // (both reads compare packed bf16 pairs: 1-2 instructions per two logits; a NaN in the row makes the
+    // window empty and the general way takes over)
+    __nv_bfloat162 m2 = __floats2bfloat162_rn(-INFINITY, -INFINITY);
+    for_each_word(row, p.vocab, vec_ok, [&](int, uint32_t w) { m2 = __hmax2_nan(m2, *reinterpret_cast<const __nv_bfloat162*>(&w)); });
+    const __nv_bfloat16 m1 = __hmax_nan(__low2bfloat16(m2), __high2bfloat16(m2));
+    uint32_t kmax = sort_key(__bfloat16_as_ushort(m1));
+    kmax = __reduce_max_sync(0xffffffffu, kmax);
+    if ((threadIdx.x & 31) == 0) hist[warp] = kmax;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const uint32_t m = __reduce_max_sync(0xffffffffu, threadIdx.x < NW ? hist[threadIdx.x] : 0u);
+      if (threadIdx.x == 0) { sel_s[0] = m; n_kept_s = 0; }
+    }
+    __syncthreads();
+    kmax = sel_s[0];
+    {
+      const uint32_t lo = kmax > 127u ? kmax - 127u : 0u;
+      const uint16_t lo_bits = (lo & 0x8000u) ? static_cast<uint16_t>(lo ^ 0x8000u) : static_cast<uint16_t>(~lo);
+      const __nv_bfloat16 t1 = __ushort_as_bfloat16(lo_bits);
+      const __nv_bfloat162 t2 = __halves2bfloat162(t1, t1);
+      auto push = [&](int c, uint16_t bits) {
+        if (c >= p.vocab) return;                             // the pad of an odd last column
+        const uint32_t slot = atomicAdd(&n_kept_s, 1u);
+        if (slot < kKeptCap) { kept_col[slot] = c; kept_bits[slot] = bits; }
+      };
+      for_each_word(row, p.vocab, vec_ok, [&](int c, uint32_t w) {
+        const uint32_t ge = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w), t2);
+        if (ge == 0u) return;
+        if (ge & 0xffffu) push(c, static_cast<uint16_t>(w & 0xffffu));
+        if (ge >> 16) push(c + 1, static_cast<uint16_t>(w >> 16));
+      });
+      __syncthreads();
+    }
+    if (n_kept_s >= static_cast<uint32_t>(k) && n_kept_s <= kKeptCap) {
+      thresh = kth_key(true);
+      compact = true;
+    } else {
+      // the general way: radix select over the whole row, then the kept entries (k of them, plus ties
+      // at the threshold) into shared memory if they fit
+      thresh = kth_key(false);
+      gather(thresh);
+      compact = n_kept_s <= kKeptCap;
+    }
   }
   const int n_kept = compact ? static_cast<int>(n_kept_s) : 0;
   // f(column, bits) for every entry with key >= thresh
   auto for_each_kept = [&](auto f) {
     if (compact) {
-      for (int i = threadIdx.x; i < n_kept; i += kSampleThreads) f(kept_col[i], kept_bits[i]);
+      for (int i = threadIdx.x; i < n_kept; i += kSampleThreads)
+        if (sort_key(kept_bits[i]) >= thresh) f(kept_col[i], kept_bits[i]);
     } else {
       for_each_logit(row, p.vocab, vec_ok, [&](int c, uint16_t bits) {
         if (sort_key(bits) >= thresh) f(c, bits);
