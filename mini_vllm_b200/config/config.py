@@ -34,6 +34,7 @@ class Config:
     kv_cache_block_size: int = 256
     gpu_memory_utilization: float = 0.5
     enable_prefix_cache: bool = False        # the reference ships with prefix caching switched off
+    enable_mixed_steps: bool = False         # extension: new prompts join a step of running decodes (scheduler.py)
 
     # executor
     use_cuda_graph: bool = True

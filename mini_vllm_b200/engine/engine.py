@@ -55,7 +55,8 @@ class Engine:
         """True when no scheduling decision depends on a sampled token's value: every request stops on
         its token budget alone and no block is published to the prefix cache."""
         no_eos = all(sp.ignore_eos for sp in sampling_params) or not self.config.eos_token_ids
-        return no_eos and not self.config.enable_prefix_cache
+        # (a mixed step takes its decode inputs from Request.tokens, so it needs them on the host)
+        return no_eos and not self.config.enable_prefix_cache and not self.config.enable_mixed_steps
 
     def _generate_pipelined(self, reqs: list[Request]) -> None:
         """The step loop without the per-step device-to-host sync (the reference blocks on ``.tolist()``

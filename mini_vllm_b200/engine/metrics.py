@@ -32,7 +32,14 @@ class Metrics:
 
     def update(self, batch: Batch) -> None:
         dt = time.perf_counter() - batch.create_time
-        if batch.type == Batch.PREFILL:
+        if batch.type == Batch.MIXED:                 # counted as a decode step that also prefilled
+            bp = len(batch.requests) - batch.num_decode
+            self.prefill_tokens += sum(len(r.tokens) - 1 - r.num_cached_tokens for r in batch.requests[:bp])
+            self.decode_steps += 1
+            self.decode_time += dt
+            self.decode_tokens += batch.num_decode
+            self.finished_request_count += sum(1 for r in batch.requests if r.finished)
+        elif batch.type == Batch.PREFILL:
             self.prefill_steps += 1
             self.prefill_time += dt
             self.prefill_tokens += sum(len(r.tokens) - r.num_cached_tokens for r in batch.requests)

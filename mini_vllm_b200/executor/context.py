@@ -30,6 +30,9 @@ class Context:
     slot_mapping: Optional[torch.Tensor] = None
     cache_seqlens: Optional[torch.Tensor] = None
     block_table: Optional[torch.Tensor] = None
+    # extension (mixed step): the last num_decode sequences of a prefill-shaped step hold one query token each
+    # and are attended by the decode kernel; cache_seqlens then holds THEIR lengths
+    num_decode: int = 0
 
     # filled by the attention layer on first use within this forward pass
     decode_plans: dict = field(default_factory=dict, repr=False, compare=False)

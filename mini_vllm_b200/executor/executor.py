@@ -137,6 +137,30 @@ class Executor:
                       block_table=out["block_table"], status=self.status)
         return out["input_ids"], ctx
 
+    def _build_mixed_input(self, requests: list[Request], num_decode: int) -> tuple[torch.Tensor, Context]:
+        """One ragged step: the first requests prefill, the last ``num_decode`` decode.  A decoding request
+        is packed as a sequence whose first ``len - 1`` tokens are cached, so the prefill packing kernel
+        lays out everything (ids, positions, slots, cu_seqlens, block table) for both parts at once."""
+        b, bp = len(requests), len(requests) - num_decode
+        seq_len, nblk, blk_off, blocks = self._per_seq(requests)
+        cached = np.fromiter((r.num_cached_tokens for r in requests), np.int32, b)
+        cached[bp:] = seq_len[bp:] - 1
+        q_len = seq_len - cached
+        t = int(q_len.sum())
+        new_tokens = np.fromiter(
+            itertools.chain(itertools.chain.from_iterable(r.tokens[r.num_cached_tokens:] for r in requests[:bp]),
+                            (r.tokens[-1] for r in requests[bp:])), np.int32, t)
+        meta = self._stage.upload([seq_len, cached, blk_off, blocks, new_tokens])
+        self.h2d_bytes += meta.numel() * 4
+        width = max(int(nblk.max()), 1)
+        out = ops.pack_prefill(meta, b, t, int(blk_off[-1]), width, self.block_size, True, self.status)
+        cu_k = out["cu_seqlens_k"]
+        ctx = Context(prefill=True, positions=out["positions"], cu_seqlens_q=out["cu_seqlens_q"], cu_seqlens_k=cu_k,
+                      slot_mapping=out["slot_mapping"], max_seqlen_q=int(q_len[:bp].max()),
+                      max_seqlen_k=int(seq_len.max()), block_table=out["block_table"], num_decode=num_decode,
+                      cache_seqlens=(cu_k[bp + 1:] - cu_k[bp:-1]).contiguous(), status=self.status)
+        return out["input_ids"], ctx
+
     def _decode_meta(self, requests: list[Request]):
         b = len(requests)
         seq_len, nblk, blk_off, blocks = self._per_seq(requests)
@@ -275,6 +299,8 @@ class Executor:
         self._step += 1
         if batch.type == Batch.PREFILL:
             input_ids, ctx = self._build_prefill_input(batch.requests)
+        elif batch.type == Batch.MIXED:
+            input_ids, ctx = self._build_mixed_input(batch.requests, batch.num_decode)
         else:
             input_ids, ctx = self._build_decode_input(batch.requests)
         logits = self.forward(ctx, input_ids)

@@ -82,7 +82,31 @@ class FlashAttention(nn.Module):
                                   k_in_place=ctx.prefill and ctx.block_table is None, status=ctx.status)
         return self._attend(ctx, q, k, v)
 
+    def _attend_mixed(self, ctx: Context, q: torch.Tensor) -> torch.Tensor:
+        """A step holding both kinds of sequence (an extension; the reference's Context is one or the
+        other): the prompts go through the prefill kernel, the single-token sequences at the end through
+        the decode kernel, both over the paged pool the write kernel has just filled."""
+        nd = ctx.num_decode
+        bp, tp = ctx.cu_seqlens_q.numel() - 1 - nd, q.shape[0] - nd
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        ops.prefill_attn(q[:tp], self.k_cache, self.v_cache, ctx.cu_seqlens_q[:bp + 1], ctx.cu_seqlens_k[:bp + 1],
+                         ctx.max_seqlen_q, self.scaling, self.window_left, block_table=ctx.block_table[:bp],
+                         out=out[:tp], status=ctx.status)
+        wl = self.window_left
+        table = ctx.block_table[bp:]
+        ws = ctx.decode_plans.get(wl)
+        if ws is None:
+            ws = _decode_workspace(q.device, nd, self.num_heads, self.head_dim, wl)
+            ops.decode_plan(ctx.cache_seqlens, wl, self.num_heads, self.num_kv_heads, self.head_dim, ws,
+                            block_table=table, block_size=self.k_cache.shape[1])
+            ctx.decode_plans[wl] = ws
+        ops.decode_attn(q[tp:], self.k_cache, self.v_cache, ctx.cache_seqlens, table, self.scaling, wl, ws, out=out[tp:],
+                        status=ctx.status)
+        return out
+
     def _attend(self, ctx: Context, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        if ctx.prefill and ctx.num_decode:
+            return self._attend_mixed(ctx, q)
         if ctx.prefill:
             if ctx.block_table is not None:        # prefix cache in play: keys come from the pool
                 return ops.prefill_attn(q, self.k_cache, self.v_cache, ctx.cu_seqlens_q, ctx.cu_seqlens_k,

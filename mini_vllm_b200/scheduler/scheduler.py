@@ -27,6 +27,7 @@ class Scheduler:
         self.max_num_batched_seqs = config.max_num_batched_seqs
         self.max_num_batched_tokens = config.max_num_batched_tokens
         self.eos_token_ids = config.eos_token_ids
+        self.mixed_steps = bool(getattr(config, "enable_mixed_steps", False))
         prefix = bool(getattr(config, "enable_prefix_cache", False))
         self.block_manager = KVCacheBlockManager(config.kv_cache_num_blocks, config.kv_cache_block_size,
                                                  support_prefix_cache=prefix, keep_last_block_uncached=prefix)
@@ -45,9 +46,11 @@ class Scheduler:
         self.block_manager.deallocate(req)
         self.waiting.appendleft(req)
 
-    def _schedule_prefill(self):
-        bm, picked, budget = self.block_manager, [], self.max_num_batched_tokens
-        while self.waiting and len(picked) < self.max_num_batched_seqs:
+    def _schedule_prefill(self, max_seqs: int | None = None, max_tokens: int | None = None):
+        bm, picked = self.block_manager, []
+        budget = self.max_num_batched_tokens if max_tokens is None else max_tokens
+        max_seqs = self.max_num_batched_seqs if max_seqs is None else max_seqs
+        while self.waiting and len(picked) < max_seqs:
             req = self.waiting[0]
             cost = len(req.tokens) - req.num_cached_tokens
             if cost > budget or not bm.can_allocate_new_block(req):
@@ -76,7 +79,20 @@ class Scheduler:
         self.running.extendleft(reversed(picked))
         return Batch(Batch.DECODE, picked)
 
+    def _schedule_mixed(self):
+        """Extension (the reference's step is prefill XOR decode, ``:83-89``): the running requests
+        decode as usual and, in the same step, prompts are admitted from the head of ``waiting`` with the
+        sequence slots and the token budget the decodes leave."""
+        decode = self._schedule_decode()
+        nd = len(decode.requests) if decode else 0
+        prefill = self._schedule_prefill(self.max_num_batched_seqs - nd, self.max_num_batched_tokens - nd)
+        if prefill is None or decode is None:
+            return prefill or decode
+        return Batch(Batch.MIXED, prefill.requests + decode.requests, num_decode=nd)
+
     def schedule(self):
+        if self.mixed_steps and self.running and self.waiting:
+            return self._schedule_mixed()
         return self._schedule_prefill() or self._schedule_decode()
 
     def update(self, batch: Batch, tokens: list[int]) -> None:

@@ -108,6 +108,11 @@ class OracleExecutor:
 
     def logits(self, batch) -> torch.Tensor:
         from . import packing
+        if batch.type == 2:                                             # a mixed step is its two halves, row order kept
+            from types import SimpleNamespace
+            bp = len(batch.requests) - batch.num_decode
+            return torch.cat([self.logits(SimpleNamespace(type=0, requests=batch.requests[:bp])),
+                              self.logits(SimpleNamespace(type=1, requests=batch.requests[bp:]))])
         dev = self.model.device
         reqs = batch.requests
         toks, blks = [r.tokens for r in reqs], [r.blocks for r in reqs]

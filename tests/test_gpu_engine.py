@@ -120,6 +120,31 @@ def test_pipelined_loop_with_preemption_matches_oracle(cuda):
     check_tokens(engine, "qwen3", prompts, params, cfg, got)
 
 
+@pytest.mark.parametrize("family,shape", [("qwen3", small_qwen3), ("gemma3", small_gemma3)])
+def test_mixed_prefill_and_decode_steps_match_oracle(cuda, family, shape):
+    """``enable_mixed_steps``: prompts are prefilled in the same step in which running requests decode
+    (one forward pass, the prefill kernel on one part of the rows and the decode kernel on the rest).
+    Few sequence slots and different output lengths, so prompts keep arriving next to decodes."""
+    g = generator(12)
+    prompts = [torch.randint(0, 2048, (int(n),), generator=g).tolist() for n in randint(g, 5, 600, 14)]
+    params = [SamplingParams(max_tokens=int(m), ignore_eos=True) for m in randint(g, 4, 40, 14)]
+    cfg = Config(hf_config=shape(), kv_cache_num_blocks=48, max_num_batched_seqs=4, max_num_batched_tokens=2048,
+                 enable_mixed_steps=True, gpu_memory_utilization=0.3, seed=6)
+    engine = Engine(cfg)
+    kinds = []
+    step = engine.step
+    def spy():
+        batch = step()
+        kinds.append(batch.type)
+        return batch
+    engine.step = spy
+    out = engine.generate(prompts, copy.deepcopy(params), use_tqdm=False)
+    got = [o["tokens"] for o in out]
+    assert [len(t) for t in got] == [sp.max_tokens for sp in params]
+    assert kinds.count(2) >= 3, "no mixed step was scheduled"
+    check_tokens(engine, family, prompts, params, cfg, got)
+
+
 def test_sampling_params_paths(cuda):
     """Temperature alone stays greedy (reference behaviour); top-k draws are seeded and reproducible."""
     g = generator(8)

@@ -111,3 +111,47 @@ def test_scheduler_trace_matches_reference(name):
     assert sch.finished
     assert [r.completion_tokens for r in reqs] == t["completions"]
     assert any(s["type"] == Batch.DECODE for s in t["steps"])
+
+
+def test_mixed_steps_admit_prompts_next_to_running_decodes():
+    """With ``enable_mixed_steps`` a step may hold prompts followed by decoding requests; every request
+    still produces exactly its tokens, the caps hold, and without the flag nothing changes."""
+    import random
+    rnd = random.Random(7)
+    prompts = [[rnd.randrange(1000) for _ in range(rnd.randrange(5, 600))] for _ in range(40)]
+    budgets = [rnd.randrange(3, 40) for _ in prompts]
+
+    def run(mixed):
+        cfg = SimpleNamespace(max_num_batched_seqs=8, max_num_batched_tokens=1024, eos_token_ids=set(),
+                              kv_cache_num_blocks=24, kv_cache_block_size=256, enable_prefix_cache=False,
+                              enable_mixed_steps=mixed)
+        sch = Scheduler(cfg)
+        reqs = [Request(p, SamplingParams(max_tokens=m, ignore_eos=True)) for p, m in zip(prompts, budgets)]
+        for r in reqs:
+            sch.submit(r)
+        kinds, steps = set(), 0
+        while not sch.finished:
+            batch = sch.schedule()
+            assert batch is not None
+            kinds.add(batch.type)
+            b, nd = len(batch.requests), batch.num_decode
+            assert 0 < b <= 8
+            if batch.type == Batch.MIXED:
+                assert 0 < nd < b
+                new_tokens = sum(len(r.tokens) - r.num_cached_tokens for r in batch.requests[:b - nd]) + nd
+                assert new_tokens <= 1024
+                assert all(r.num_completion_tokens == 0 for r in batch.requests[:b - nd])
+                assert all(r.num_completion_tokens > 0 for r in batch.requests[b - nd:])
+                assert len({r.id for r in batch.requests}) == b
+            # every scheduled request owns the blocks its tokens need
+            assert all(len(r.blocks) * 256 >= len(r.tokens) for r in batch.requests)
+            sch.update(batch, [1] * b)
+            steps += 1
+        assert [r.num_completion_tokens for r in reqs] == budgets
+        return kinds, steps
+
+    kinds, steps = run(True)
+    assert Batch.MIXED in kinds
+    plain_kinds, plain_steps = run(False)
+    assert Batch.MIXED not in plain_kinds
+    assert steps < plain_steps                              # prompts no longer cost steps of their own
