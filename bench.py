@@ -434,7 +434,11 @@ def main():
         all_reqs = config5_requests(seed=0, n=512 * world)
     else:
         all_reqs = config2_requests(seed=0, n=64 * world)
-    mine = [all_reqs[i] for i in partition_by_tokens([len(r.prompt) + r.max_tokens for r in all_reqs], world)[rank]]
+    # Split by token count - the K/V tokens a request will have read by its end, one context per generated
+    # token: out * (prompt + out / 2).  (The plain prompt + output sum balances the token totals to 0.01 % but
+    # leaves the replicas' attention work 3 % apart, and the job is bound by the slowest replica.)
+    weights = [r.max_tokens * (2 * len(r.prompt) + r.max_tokens) // 2 for r in all_reqs]
+    mine = [all_reqs[i] for i in partition_by_tokens(weights, world)[rank]]
     engine = build_engine(local_rank, args.workload)
     dev = engine.executor.device
 
