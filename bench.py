@@ -49,10 +49,30 @@ from mini_vllm_b200.workloads import (GEMMA3_1B, QWEN3_0P6B, config2_requests, c
 
 METRIC = "ragged prefill+decode tokens/s (Qwen3-0.6B shapes, continuous batching, greedy)"
 WORKLOADS = {
-    "config5": "config5 share: Qwen3-0.6B random-init, 512 req/GPU (4096 over 8 GPUs), prompt log-U[32,4096], "
-               "output U[64,1024], continuous batching",
+    "config5": "config5 share: Qwen3-0.6B random-init, 512 req/GPU (one of the 8 shares of 4096 requests per GPU), "
+               "prompt log-U[32,4096], output U[64,1024], continuous batching",
     "config2": "config2: Qwen3-0.6B random-init, 64 req/GPU, prompt U[100,1024], total<=1024, continuous batching",
 }
+
+
+def workload_requests(workload: str, world: int = 1, rank: int = 0):
+    """The requests of one replica.
+
+    Requests are split by token count - the K/V tokens a request will have read by its end, one context per
+    generated token: out * (prompt + out / 2).  (The plain prompt + output sum balances the token totals to
+    0.01 % but leaves the replicas' attention work 3 % apart, and a job is bound by its slowest replica.)
+    Config 5 is 4096 requests over 8 GPUs: it is cut into its 8 shares once, and a run on N GPUs takes the
+    first N of them, so every replica's job is the same at every N."""
+    kv_tokens = lambda r: r.max_tokens * (2 * len(r.prompt) + r.max_tokens) // 2
+    if workload == "config5" and world <= 8:
+        from mini_vllm_b200.workloads import config5_requests
+        all_reqs, parts = config5_requests(seed=0, n=4096), 8
+    elif workload == "config5":
+        from mini_vllm_b200.workloads import config5_requests
+        all_reqs, parts = config5_requests(seed=0, n=512 * world), world
+    else:
+        all_reqs, parts = config2_requests(seed=0, n=64 * world), world
+    return [all_reqs[i] for i in partition_by_tokens([kv_tokens(r) for r in all_reqs], parts)[rank]]
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -334,11 +354,7 @@ def cpu_reference_sample(workload: str = "config5", budget_s: float = 20.0, seed
     omodel = OracleModel(weights, hf, "qwen3", 160, 256, device="cpu")
     ex = OracleExecutor(omodel, 256)
     n_req, n_dec = 8, 48
-    if workload == "config5":
-        from mini_vllm_b200.workloads import config5_requests
-        reqs = config5_requests(seed, n=512)[:n_req]
-    else:
-        reqs = config2_requests(seed)[:n_req]
+    reqs = workload_requests(workload)[:n_req]
     sch = Scheduler(cfg)
     rs = [Request(r.prompt, SamplingParams(max_tokens=n_dec, ignore_eos=True)) for r in reqs]
     for r in rs:
@@ -404,12 +420,7 @@ def main():
         from mini_vllm_b200.engine.engine import Engine
         torch.cuda.set_device(0)
         eng = Engine(dataclasses.replace(build_config(args.workload), use_cuda_graph=False))   # every kernel its own launch
-        if args.workload == "config5":
-            from mini_vllm_b200.workloads import config5_requests
-            reqs = config5_requests(seed=0, n=512)
-        else:
-            reqs = config2_requests(0)
-        for r in reqs:
+        for r in workload_requests(args.workload):
             eng.submit(r.prompt, SamplingParams(max_tokens=r.max_tokens, ignore_eos=True))
         done = 0
         while done < args.engine_steps:
@@ -429,16 +440,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks, peak_kind = measured_peaks()
 
-    if args.workload == "config5":
-        from mini_vllm_b200.workloads import config5_requests
-        all_reqs = config5_requests(seed=0, n=512 * world)
-    else:
-        all_reqs = config2_requests(seed=0, n=64 * world)
-    # Split by token count - the K/V tokens a request will have read by its end, one context per generated
-    # token: out * (prompt + out / 2).  (The plain prompt + output sum balances the token totals to 0.01 % but
-    # leaves the replicas' attention work 3 % apart, and the job is bound by the slowest replica.)
-    weights = [r.max_tokens * (2 * len(r.prompt) + r.max_tokens) // 2 for r in all_reqs]
-    mine = [all_reqs[i] for i in partition_by_tokens(weights, world)[rank]]
+    mine = workload_requests(args.workload, world, rank)
     engine = build_engine(local_rank, args.workload)
     dev = engine.executor.device
 
