@@ -52,28 +52,42 @@ class Engine:
     RUN_AHEAD = 2         # steps the host may be ahead of the device results
 
     def _schedule_is_token_independent(self, sampling_params) -> bool:
-        """True when no scheduling decision depends on a sampled token's value: every request stops on
-        its token budget alone and no block is published to the prefix cache."""
-        no_eos = all(sp.ignore_eos for sp in sampling_params) or not self.config.eos_token_ids
-        # (a mixed step takes its decode inputs from Request.tokens, so it needs them on the host)
-        return no_eos and not self.config.enable_prefix_cache and not self.config.enable_mixed_steps
+        """True when the step loop may run ahead of the sampled tokens: no block is published to the prefix
+        cache (its hash needs the tokens) and decode inputs need not come from the host (mixed steps).
+        Stopping on EOS does not prevent it: a request that has emitted EOS is found out a few steps late,
+        and what it generated past that point is dropped."""
+        return not self.config.enable_prefix_cache and not self.config.enable_mixed_steps
 
     def _generate_pipelined(self, reqs: list[Request]) -> None:
         """The step loop without the per-step device-to-host sync (the reference blocks on ``.tolist()``
         every step, executor.py:193-195).  Sampled ids stay on the device, where the next decode packing
-        picks them up; they reach ``Request.tokens`` a few steps late through a pinned buffer."""
+        picks them up; they reach ``Request.tokens`` a few steps late through a pinned buffer.
+
+        Requests that stop on EOS are scheduled speculatively: until the EOS token has reached the host
+        (at most ``RUN_AHEAD`` steps) the request keeps decoding; then it is cut back to the EOS token and
+        its blocks are freed.  Freeing while those extra steps may still be in flight is safe because every
+        step runs on one stream: whoever gets the blocks next writes them after the stragglers have."""
         ex, sch = self.executor, self.scheduler
+        eos = self.config.eos_token_ids or ()
         slot_of = {r.id: i for i, r in enumerate(reqs)}
         ex.ensure_token_table(len(reqs))
         unresolved = dict.fromkeys(slot_of, 0)
+        stopped_at: dict[int, int] = {}               # request id -> number of tokens it really has (EOS included)
         pending: deque = deque()
 
         def resolve(item) -> None:
             batch_reqs, positions, host, event = item
             event.synchronize()
             for r, pos, tok in zip(batch_reqs, positions, host.tolist()):
-                r.tokens[pos] = tok
                 unresolved[r.id] -= 1
+                if r.id in stopped_at:                # a step that ran past the request's EOS
+                    continue
+                r.tokens[pos] = tok
+                if eos and tok in eos and not r.sampling_params.ignore_eos:
+                    stopped_at[r.id] = pos + 1
+                    del r.tokens[pos + 1:]
+                    if not r.finished:
+                        sch.stop(r)
 
         self._job_start = torch.cuda.Event(enable_timing=True)
         self._job_start.record()
@@ -84,6 +98,10 @@ class Engine:
             if batch.type == Batch.PREFILL and any(unresolved[r.id] for r in batch.requests):
                 while pending:                      # a preempted request is re-prefilled from its real tokens
                     resolve(pending.popleft())
+                if any(r.finished for r in batch.requests):   # ... unless those tokens ended in an EOS
+                    batch.requests = [r for r in batch.requests if not r.finished]
+                    if not batch.requests:
+                        continue
             slots = np.fromiter((slot_of[r.id] for r in batch.requests), np.int32, len(batch.requests))
             host, event = ex.launch(batch, slots)
             positions = [len(r.tokens) for r in batch.requests]

@@ -95,6 +95,15 @@ class Scheduler:
             return self._schedule_mixed()
         return self._schedule_prefill() or self._schedule_decode()
 
+    def stop(self, req: Request) -> None:
+        """Ends a request from outside a step (the pipelined loop learns of an EOS a few steps late)."""
+        if req.state == Request.RUNNING:
+            self.block_manager.deallocate(req)
+            self.running.remove(req)
+        elif req.state == Request.WAITING:            # preempted in the meantime: it holds no blocks
+            self.waiting.remove(req)
+        req.state = Request.FINISHED
+
     def update(self, batch: Batch, tokens: list[int]) -> None:
         bm = self.block_manager
         for req, token in zip(batch.requests, tokens):

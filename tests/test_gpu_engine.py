@@ -145,6 +145,36 @@ def test_mixed_prefill_and_decode_steps_match_oracle(cuda, family, shape):
     check_tokens(engine, family, prompts, params, cfg, got)
 
 
+def test_pipelined_loop_stops_on_eos_like_the_oracle(cuda):
+    """EOS stopping under the pipelined loop: a request that emitted EOS keeps decoding until the token has
+    reached the host, then is cut back.  A third of the vocabulary is EOS so that requests stop at scattered
+    points; some requests ignore EOS; the pool is tight enough for preemptions."""
+    g = generator(13)
+    prompts = [torch.randint(0, 2048, (int(n),), generator=g).tolist() for n in randint(g, 20, 500, 16)]
+    params = [SamplingParams(max_tokens=60, ignore_eos=(i % 4 == 3)) for i in range(len(prompts))]
+    shape = small_qwen3()
+    shape.eos_token_id = [i for i in range(2048) if i % 3 == 0]
+    cfg = Config(hf_config=shape, kv_cache_num_blocks=12, max_num_batched_seqs=6, max_num_batched_tokens=4096,
+                 gpu_memory_utilization=0.3, seed=9)
+    assert cfg.eos_token_ids
+    engine = Engine(cfg)
+    assert engine._schedule_is_token_independent(params)
+    out = engine.generate(prompts, copy.deepcopy(params), use_tqdm=False)
+    got = [o["tokens"] for o in out]
+    eos = set(cfg.eos_token_ids)
+    stopped = 0
+    for toks, sp in zip(got, params):
+        assert 1 <= len(toks) <= 60 and min(toks) >= 0
+        if sp.ignore_eos:
+            assert len(toks) == 60
+        else:
+            assert all(t not in eos for t in toks[:-1]), "tokens were kept past an EOS"
+            assert len(toks) == 60 or toks[-1] in eos
+            stopped += toks[-1] in eos and len(toks) < 60
+    assert stopped >= 4
+    check_tokens(engine, "qwen3", prompts, params, cfg, got)
+
+
 def test_sampling_params_paths(cuda):
     """Temperature alone stays greedy (reference behaviour); top-k draws are seeded and reproducible."""
     g = generator(8)

@@ -155,3 +155,29 @@ def test_mixed_steps_admit_prompts_next_to_running_decodes():
     plain_kinds, plain_steps = run(False)
     assert Batch.MIXED not in plain_kinds
     assert steps < plain_steps                              # prompts no longer cost steps of their own
+
+
+def test_stop_ends_a_running_or_a_preempted_request():
+    """``Scheduler.stop`` (used when an EOS is learnt of late): blocks go back, queues forget the request."""
+    cfg = SimpleNamespace(max_num_batched_seqs=4, max_num_batched_tokens=4096, eos_token_ids=set(),
+                          kv_cache_num_blocks=8, kv_cache_block_size=256, enable_prefix_cache=False)
+    sch = Scheduler(cfg)
+    reqs = [Request(list(range(300)), SamplingParams(max_tokens=50, ignore_eos=True)) for _ in range(3)]
+    for r in reqs:
+        sch.submit(r)
+    batch = sch.schedule()
+    assert batch.type == Batch.PREFILL and len(batch.requests) == 3
+    sch.update(batch, [1, 1, 1])
+    free_before = len(sch.block_manager.free_block_ids)
+    sch.stop(reqs[0])
+    assert reqs[0].finished and reqs[0] not in sch.running
+    assert len(sch.block_manager.free_block_ids) == free_before + 2
+    sch.preempt(reqs[2]); sch.running.remove(reqs[2])
+    assert reqs[2] in sch.waiting
+    sch.stop(reqs[2])
+    assert reqs[2].finished and reqs[2] not in sch.waiting
+    while not sch.finished:
+        b = sch.schedule()
+        assert [r.id for r in b.requests] == [reqs[1].id]
+        sch.update(b, [1])
+    assert reqs[1].num_completion_tokens == 50
