@@ -129,10 +129,11 @@ def build_config(workload: str = "config5") -> Config:
                   max_num_batched_tokens=16384, gpu_memory_utilization=0.5, use_cuda_graph=True, seed=0)
 
 
-def build_engine(local_rank: int, workload: str = "config5"):
+def build_engine(local_rank: int, workload: str = "config5", mixed_steps: bool = False):
+    import dataclasses
     from mini_vllm_b200.engine.engine import Engine
     torch.cuda.set_device(local_rank)
-    return Engine(build_config(workload))
+    return Engine(dataclasses.replace(build_config(workload), enable_mixed_steps=mixed_steps))
 
 
 def run_job(engine, reqs, record_contexts=None):
@@ -406,6 +407,8 @@ def main():
                          "U[64,1024]; config2: 64 requests per GPU, prompt U[100,1024], total <= 1024")
     ap.add_argument("--kernel-legs", action="store_true",
                     help="profiling aid: only the fixed single-layer kernel cases (one 2.3 GB pool), then exit")
+    ap.add_argument("--mixed-steps", action="store_true",
+                    help="variant: prompts join steps of running decodes (Config.enable_mixed_steps)")
     ap.add_argument("--engine-steps", type=int, default=0,
                     help="profiling aid: prefill + N decode steps of the workload without CUDA graphs, then exit")
     args = ap.parse_args()
@@ -441,7 +444,7 @@ def main():
     peaks, peak_kind = measured_peaks()
 
     mine = workload_requests(args.workload, world, rank)
-    engine = build_engine(local_rank, args.workload)
+    engine = build_engine(local_rank, args.workload, mixed_steps=args.mixed_steps)
     dev = engine.executor.device
 
     def sync_all():
@@ -498,7 +501,7 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(cuda_ms_max / args.steps, 2), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOADS[args.workload], "requests_per_gpu": len(mine), "parallelism": f"replicas x{world}",
+            "config": {"workload": WORKLOADS[args.workload] + (", mixed steps" if args.mixed_steps else ""), "requests_per_gpu": len(mine), "parallelism": f"replicas x{world}",
                        "l2": "KV pool (28 layers, >126 MB per step) exceeds L2; kernel legs rotate distinct pools",
                        "tokens_per_step_all_gpus": int(tok_all / args.steps)},
             "e2e": {"value": round(tok_all / (wall_ms_max * 1e-3), 1), "unit": "tokens/s",

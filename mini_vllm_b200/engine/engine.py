@@ -53,10 +53,10 @@ class Engine:
 
     def _schedule_is_token_independent(self, sampling_params) -> bool:
         """True when the step loop may run ahead of the sampled tokens: no block is published to the prefix
-        cache (its hash needs the tokens) and decode inputs need not come from the host (mixed steps).
-        Stopping on EOS does not prevent it: a request that has emitted EOS is found out a few steps late,
-        and what it generated past that point is dropped."""
-        return not self.config.enable_prefix_cache and not self.config.enable_mixed_steps
+        cache (its hash needs the tokens).  Stopping on EOS does not prevent it: a request that has emitted
+        EOS is found out a few steps late, and what it generated past that point is dropped.  A mixed step
+        takes its decode inputs from ``Request.tokens``, so the loop catches up with the device before one."""
+        return not self.config.enable_prefix_cache
 
     def _generate_pipelined(self, reqs: list[Request]) -> None:
         """The step loop without the per-step device-to-host sync (the reference blocks on ``.tolist()``
@@ -95,13 +95,18 @@ class Engine:
             batch = sch.schedule()
             if batch is None:
                 raise RuntimeError("nothing can be scheduled: a request needs more KV blocks than the pool holds")
-            if batch.type == Batch.PREFILL and any(unresolved[r.id] for r in batch.requests):
+            if batch.type != Batch.DECODE and any(unresolved[r.id] for r in batch.requests):
                 while pending:                      # a preempted request is re-prefilled from its real tokens
                     resolve(pending.popleft())
                 if any(r.finished for r in batch.requests):   # ... unless those tokens ended in an EOS
-                    batch.requests = [r for r in batch.requests if not r.finished]
-                    if not batch.requests:
+                    bp = len(batch.requests) - (batch.num_decode if batch.type == Batch.MIXED else 0)
+                    head = [r for r in batch.requests[:bp] if not r.finished]
+                    tail = [r for r in batch.requests[bp:] if not r.finished]
+                    if not head and not tail:
                         continue
+                    batch.requests, batch.num_decode = head + tail, len(tail)
+                    if batch.type == Batch.MIXED and not (head and tail):
+                        batch.type = Batch.PREFILL if head else Batch.DECODE
             slots = np.fromiter((slot_of[r.id] for r in batch.requests), np.int32, len(batch.requests))
             host, event = ex.launch(batch, slots)
             positions = [len(r.tokens) for r in batch.requests]

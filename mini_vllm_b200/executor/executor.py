@@ -137,7 +137,7 @@ class Executor:
                       block_table=out["block_table"], status=self.status)
         return out["input_ids"], ctx
 
-    def _build_mixed_input(self, requests: list[Request], num_decode: int) -> tuple[torch.Tensor, Context]:
+    def _build_mixed_input(self, requests: list[Request], num_decode: int, slots: np.ndarray | None = None):
         """One ragged step: the first requests prefill, the last ``num_decode`` decode.  A decoding request
         is packed as a sequence whose first ``len - 1`` tokens are cached, so the prefill packing kernel
         lays out everything (ids, positions, slots, cu_seqlens, block table) for both parts at once."""
@@ -150,7 +150,7 @@ class Executor:
         new_tokens = np.fromiter(
             itertools.chain(itertools.chain.from_iterable(r.tokens[r.num_cached_tokens:] for r in requests[:bp]),
                             (r.tokens[-1] for r in requests[bp:])), np.int32, t)
-        meta = self._stage.upload([seq_len, cached, blk_off, blocks, new_tokens])
+        meta = self._stage.upload([seq_len, cached, blk_off, blocks, new_tokens] + ([slots] if slots is not None else []))
         self.h2d_bytes += meta.numel() * 4
         width = max(int(nblk.max()), 1)
         out = ops.pack_prefill(meta, b, t, int(blk_off[-1]), width, self.block_size, True, self.status)
@@ -159,7 +159,9 @@ class Executor:
                       slot_mapping=out["slot_mapping"], max_seqlen_q=int(q_len[:bp].max()),
                       max_seqlen_k=int(seq_len.max()), block_table=out["block_table"], num_decode=num_decode,
                       cache_seqlens=(cu_k[bp + 1:] - cu_k[bp:-1]).contiguous(), status=self.status)
-        return out["input_ids"], ctx
+        if slots is None:
+            return out["input_ids"], ctx
+        return out["input_ids"], ctx, meta[meta.numel() - b:]
 
     def _decode_meta(self, requests: list[Request]):
         b = len(requests)
@@ -249,6 +251,9 @@ class Executor:
                           max_seqlen_q=int(q_len.max()), max_seqlen_k=int(seq_len.max()),
                           block_table=out["block_table"], status=self.status)
             input_ids = out["input_ids"]
+        elif batch.type == Batch.MIXED:                # (its decode inputs come from Request.tokens: the caller has
+            input_ids, ctx, slots_dev = self._build_mixed_input(reqs, batch.num_decode, slots)   # resolved them)
+            meta = None
         else:
             seq_len, nblk, blk_off, blocks = self._per_seq(reqs)
             meta = self._stage.upload([seq_len, blk_off, blocks, np.zeros(b, np.int32), slots])
@@ -269,7 +274,8 @@ class Executor:
                                 prev_sampled=self.token_table, status=self.status)
                 ctx = Context(prefill=False, positions=pos, slot_mapping=slot, cache_seqlens=lens, block_table=table,
                               status=self.status)
-        self.h2d_bytes += meta.numel() * 4
+        if meta is not None:
+            self.h2d_bytes += meta.numel() * 4
         logits = self.forward(ctx, input_ids)
         temperatures, top_k, top_p = self._build_sample_input(reqs)
         tokens = self.sampler(logits, temperatures, top_p=top_p, top_k=top_k, scatter_table=self.token_table,

@@ -132,12 +132,11 @@ def test_mixed_prefill_and_decode_steps_match_oracle(cuda, family, shape):
                  enable_mixed_steps=True, gpu_memory_utilization=0.3, seed=6)
     engine = Engine(cfg)
     kinds = []
-    step = engine.step
-    def spy():
-        batch = step()
+    launch = engine.executor.launch
+    def spy(batch, slots):
         kinds.append(batch.type)
-        return batch
-    engine.step = spy
+        return launch(batch, slots)
+    engine.executor.launch = spy
     out = engine.generate(prompts, copy.deepcopy(params), use_tqdm=False)
     got = [o["tokens"] for o in out]
     assert [len(t) for t in got] == [sp.max_tokens for sp in params]
