@@ -272,6 +272,26 @@ def kernel_extras(dev, peaks, nl=4):
     out["prefill_attn_config3"] = {"TFLOP/s": round(tf, 1), "us": round(ms * 1e3, 1), "flops": fl,
                                    "frac_of_measured_bf16": round(tf / peaks["bf16_tflops"], 4)}
     del pools
+    # the same kernel on long and on short prompts (dense K/V): 4 x 8192 and 32 x 1024 tokens
+    for name, (nseq, slen) in (("prefill_attn_4x8192", (4, 8192)), ("prefill_attn_32x1024", (32, 1024))):
+        lens_p = [slen] * nseq
+        qd = torch.randn(nseq * slen, hq, d, device=dev, dtype=torch.bfloat16)
+        kd = torch.randn(nseq * slen, hkv, d, device=dev, dtype=torch.bfloat16)
+        vd = torch.randn(nseq * slen, hkv, d, device=dev, dtype=torch.bfloat16)
+        cd = cu(lens_p)
+        for _ in range(3):
+            ops.prefill_attn(qd, kd, vd, cd, cd, slen, d ** -0.5, -1)
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(11)]
+        evs[0].record()
+        for i in range(10):
+            ops.prefill_attn(qd, kd, vd, cd, cd, slen, d ** -0.5, -1)
+            evs[i + 1].record()
+        torch.cuda.synchronize()
+        ms = statistics.median(evs[i].elapsed_time(evs[i + 1]) for i in range(10))
+        fl = prefill_flops(QWEN3_0P6B, lens_p, [0] * nseq)
+        out[name] = {"TFLOP/s": round(fl / ms / 1e9, 1), "us": round(ms * 1e3, 1), "flops": fl,
+                     "frac_of_measured_bf16": round(fl / ms / 1e9 / peaks["bf16_tflops"], 4)}
+        del qd, kd, vd
     # Gemma3-1B shapes (4 q heads, 1 kv head, head_dim 256), 128 sequences, contexts U[512,4096]:
     # a global layer and a sliding-window-512 layer (window layers count only the visible keys)
     g4, _ = config4()
