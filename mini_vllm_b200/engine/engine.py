@@ -89,8 +89,10 @@ class Engine:
                     if not r.finished:
                         sch.stop(r)
 
-        self._job_start = torch.cuda.Event(enable_timing=True)
-        self._job_start.record()
+        timed = torch.cuda.is_available()             # (the loop itself is host logic and also runs without a GPU)
+        if timed:
+            self._job_start = torch.cuda.Event(enable_timing=True)
+            self._job_start.record()
         while not self.finished:
             batch = sch.schedule()
             if batch is None:
@@ -117,8 +119,9 @@ class Engine:
             pending.append((list(batch.requests), positions, host, event))
             while len(pending) > self.RUN_AHEAD:
                 resolve(pending.popleft())
-        self._job_end = torch.cuda.Event(enable_timing=True)
-        self._job_end.record()
+        if timed:
+            self._job_end = torch.cuda.Event(enable_timing=True)
+            self._job_end.record()
         while pending:
             resolve(pending.popleft())
 
