@@ -52,11 +52,11 @@ class Engine:
     RUN_AHEAD = 2         # steps the host may be ahead of the device results
 
     def _schedule_is_token_independent(self, sampling_params) -> bool:
-        """True when the step loop may run ahead of the sampled tokens: no block is published to the prefix
-        cache (its hash needs the tokens).  Stopping on EOS does not prevent it: a request that has emitted
-        EOS is found out a few steps late, and what it generated past that point is dropped.  A mixed step
-        takes its decode inputs from ``Request.tokens``, so the loop catches up with the device before one."""
-        return not self.config.enable_prefix_cache
+        """True when the step loop may run ahead of the sampled tokens - always, by now: a request that has
+        emitted EOS is found out a few steps late and what it generated past that point is dropped; a block
+        is published to the prefix cache when its last tokens have reached the host; a mixed step takes its
+        decode inputs from ``Request.tokens``, so the loop catches up with the device before one."""
+        return True
 
     def _generate_pipelined(self, reqs: list[Request]) -> None:
         """The step loop without the per-step device-to-host sync (the reference blocks on ``.tolist()``
@@ -69,6 +69,7 @@ class Engine:
         step runs on one stream: whoever gets the blocks next writes them after the stragglers have."""
         ex, sch = self.executor, self.scheduler
         eos = self.config.eos_token_ids or ()
+        prefix_cache, block_size = bool(self.config.enable_prefix_cache), self.config.kv_cache_block_size
         slot_of = {r.id: i for i, r in enumerate(reqs)}
         ex.ensure_token_table(len(reqs))
         unresolved = dict.fromkeys(slot_of, 0)
@@ -83,6 +84,8 @@ class Engine:
                 if r.id in stopped_at:                # a step that ran past the request's EOS
                     continue
                 r.tokens[pos] = tok
+                if prefix_cache and (pos + 1) % block_size == 0:
+                    sch.block_manager.cache_block_at(r, (pos + 1) // block_size - 1)
                 if eos and tok in eos and not r.sampling_params.ignore_eos:
                     stopped_at[r.id] = pos + 1
                     del r.tokens[pos + 1:]
@@ -114,7 +117,7 @@ class Engine:
             positions = [len(r.tokens) for r in batch.requests]
             for r in batch.requests:
                 unresolved[r.id] += 1
-            sch.update(batch, [self.PLACEHOLDER] * len(batch.requests))
+            sch.update(batch, [self.PLACEHOLDER] * len(batch.requests), defer_cache=True)
             self.metrics.update(batch)
             pending.append((list(batch.requests), positions, host, event))
             while len(pending) > self.RUN_AHEAD:

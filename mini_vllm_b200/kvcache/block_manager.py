@@ -144,6 +144,25 @@ class KVCacheBlockManager:
         req.blocks = []
         req.num_cached_tokens = 0
 
+    def cache_block_at(self, req: Request, index: int) -> None:
+        """Publish block ``index`` of the request, which has become full some steps ago (the pipelined
+        engine learns a block's last tokens late).  Nothing happens if the request has lost the block in
+        the meantime (finished or preempted) or the block before it was never published."""
+        if not self.support_prefix_cache or index >= len(req.blocks) or len(req.tokens) < (index + 1) * self.block_size:
+            return
+        bid = req.blocks[index]
+        if self._hash[bid] != NO_HASH:
+            return
+        prefix = self._hash[req.blocks[index - 1]] if index > 0 else NO_HASH
+        if index > 0 and prefix == NO_HASH:
+            return
+        content = np.asarray(req.tokens[index * self.block_size:(index + 1) * self.block_size], dtype="<i4").tobytes()
+        h = xxhash.xxh64()
+        if prefix != NO_HASH:
+            h.update(prefix.to_bytes(8, "little"))
+        h.update(content)
+        self._publish(bid, h.intdigest(), content)
+
     def cache_block_if_needed(self, req: Request) -> None:
         """Publish the request's last block once it is full (block_manager.py:144-158)."""
         if not self.support_prefix_cache or len(req.tokens) % self.block_size:

@@ -104,7 +104,9 @@ class Scheduler:
             self.waiting.remove(req)
         req.state = Request.FINISHED
 
-    def update(self, batch: Batch, tokens: list[int]) -> None:
+    def update(self, batch: Batch, tokens: list[int], defer_cache: bool = False) -> None:
+        """``defer_cache``: the tokens are placeholders (pipelined engine); blocks that fill up are published
+        later, by ``block_manager.cache_block_at``, when their tokens are known."""
         bm = self.block_manager
         for req, token in zip(batch.requests, tokens):
             req.append_output_token(token)
@@ -114,5 +116,5 @@ class Scheduler:
                 req.state = Request.FINISHED
                 bm.deallocate(req)
                 self.running.remove(req)
-            else:
+            elif not defer_cache:
                 bm.cache_block_if_needed(req)
