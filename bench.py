@@ -358,6 +358,50 @@ def kernel_extras(dev, peaks, nl=4):
     return out
 
 
+def config3_engine_step(mixed: bool) -> dict:
+    """Config 3 through the engine (28 layers): 240 requests decoding at contexts U[128,4096] when 16 prompts
+    arrive, 8 of them sharing a resident 512-token prefix (prefix cache on).  With mixed steps that is ONE
+    forward pass; the reference's scheduler makes it a prefill step followed by a decode step."""
+    import dataclasses
+    from mini_vllm_b200.engine.engine import Engine
+    case, g = config3()
+    cfg = Config(hf_config=qwen3_shape(), kv_cache_num_blocks=2400, max_num_batched_seqs=512, max_graph_batch_size=256,
+                 max_num_batched_tokens=20480, enable_prefix_cache=True, enable_mixed_steps=mixed,
+                 gpu_memory_utilization=0.85, use_cuda_graph=True, seed=0)
+    eng = Engine(cfg)
+    vocab = cfg.hf_config.vocab_size
+    tok = lambda n: torch.randint(0, vocab, (int(n),), generator=g).tolist()
+    long_run = SamplingParams(max_tokens=4096, ignore_eos=True)
+    shared = tok(512)
+    warm = eng.submit(shared + tok(8), SamplingParams(max_tokens=1, ignore_eos=True))   # leaves the prefix resident
+    while not eng.finished:
+        eng.step()
+    for c in case.decode_ctx:                      # the decoding population: prompts one token short of the context
+        eng.submit(tok(c - 1), long_run)
+    while eng.scheduler.waiting:
+        eng.step()
+    for _ in range(3):                             # settle: a few decode steps (graphs warm)
+        eng.step()
+    for i, (n, c) in enumerate(zip(case.prefill_lens, case.prefill_cached)):
+        eng.submit((shared if c else []) + tok(n - c), long_run)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    steps, new_tokens, kinds = 0, 0, []
+    while eng.scheduler.waiting or (not mixed and kinds[-1] != 1):   # the plain scheduler needs a decode step after
+        b = eng.step()
+        kinds.append(b.type)
+        bp = len(b.requests) - b.num_decode
+        new_tokens += sum(len(r.tokens) - 1 - r.num_cached_tokens for r in b.requests[:bp]) + b.num_decode
+        steps += 1
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    eng.executor.check_device_status()
+    return {"mixed_steps": mixed, "steps": steps, "step_types": kinds, "ms": round(ms, 3), "tokens": new_tokens,
+            "tokens_per_s": round(new_tokens / ms * 1e3, 1)}
+
+
 # ---- CPU leg: the oracle restatement of the reference path on the host cores ------------------------
 def cpu_reference_sample(workload: str = "config5", budget_s: float = 20.0, seed: int = 0):
     """Prefill + decode of a few config-2 requests through the oracle model on CPU; returns tok/s."""
@@ -429,11 +473,22 @@ def main():
                     help="profiling aid: only the fixed single-layer kernel cases (one 2.3 GB pool), then exit")
     ap.add_argument("--mixed-steps", action="store_true",
                     help="variant: prompts join steps of running decodes (Config.enable_mixed_steps)")
+    ap.add_argument("--config3-step", action="store_true",
+                    help="engine-level config 3: 16 prefix-cached prompts arriving among 240 decodes, as one mixed "
+                         "step and as the reference's two steps")
     ap.add_argument("--engine-steps", type=int, default=0,
                     help="profiling aid: prefill + N decode steps of the workload without CUDA graphs, then exit")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.config3_step:
+        torch.cuda.set_device(0)
+        out = []
+        for mixed in (True, False):
+            out.append(config3_engine_step(mixed))
+            torch.cuda.empty_cache()
+        print(json.dumps({"config3_engine_step": out}))
+        return
     if args.kernel_legs:
         peaks, _ = measured_peaks()
         print(json.dumps(kernel_extras(torch.device("cuda", 0), peaks, nl=1)))
