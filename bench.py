@@ -402,6 +402,30 @@ def config3_engine_step(mixed: bool) -> dict:
             "tokens_per_s": round(new_tokens / ms * 1e3, 1)}
 
 
+def config4_engine_step() -> dict:
+    """Config 4 through the engine: Gemma3-1B shapes (26 layers, 4 global / 22 window-512), 128 requests
+    decoding at contexts U[512,4096].  Device time of a decode step = (job with 65 generated tokens - job with
+    1) / 64, both through the pipelined loop with CUDA graphs."""
+    from mini_vllm_b200.config import gemma3_shape
+    from mini_vllm_b200.engine.engine import Engine
+    case, g = config4()
+    cfg = Config(hf_config=gemma3_shape(), kv_cache_num_blocks=1400, max_num_batched_seqs=128, max_graph_batch_size=128,
+                 max_num_batched_tokens=16384, gpu_memory_utilization=0.85, use_cuda_graph=True, seed=0)
+    eng = Engine(cfg)
+    vocab = cfg.hf_config.vocab_size
+    prompts = [torch.randint(0, vocab, (int(c) - 1,), generator=g).tolist() for c in case.decode_ctx]
+    times = {}
+    for n in (1, 65, 1, 65):
+        eng.generate(prompts, SamplingParams(max_tokens=n, ignore_eos=True), use_tqdm=False)
+        times[n] = eng.last_job_device_ms
+    step_ms = (times[65] - times[1]) / 64
+    ctx_mid = [c + 32 for c in case.decode_ctx]
+    byts = 4 * decode_kv_bytes(GEMMA3_1B, ctx_mid, -1) + 22 * decode_kv_bytes(GEMMA3_1B, ctx_mid, 512)
+    return {"decode_step_ms": round(step_ms, 4), "sequences": len(prompts), "kv_bytes_per_step": byts,
+            "kv_GB/s_over_whole_step": round(byts / step_ms / 1e6, 1), "tokens_per_s": round(len(prompts) / step_ms * 1e3, 1),
+            "prefill_job_ms": round(times[1], 2)}
+
+
 # ---- CPU leg: the oracle restatement of the reference path on the host cores ------------------------
 def cpu_reference_sample(workload: str = "config5", budget_s: float = 20.0, seed: int = 0):
     """Prefill + decode of a few config-2 requests through the oracle model on CPU; returns tok/s."""
@@ -476,6 +500,8 @@ def main():
     ap.add_argument("--config3-step", action="store_true",
                     help="engine-level config 3: 16 prefix-cached prompts arriving among 240 decodes, as one mixed "
                          "step and as the reference's two steps")
+    ap.add_argument("--config4-step", action="store_true",
+                    help="engine-level config 4: a decode step of 128 sequences on Gemma3-1B shapes")
     ap.add_argument("--engine-steps", type=int, default=0,
                     help="profiling aid: prefill + N decode steps of the workload without CUDA graphs, then exit")
     args = ap.parse_args()
@@ -488,6 +514,10 @@ def main():
             out.append(config3_engine_step(mixed))
             torch.cuda.empty_cache()
         print(json.dumps({"config3_engine_step": out}))
+        return
+    if args.config4_step:
+        torch.cuda.set_device(0)
+        print(json.dumps({"config4_engine_step": config4_engine_step()}))
         return
     if args.kernel_legs:
         peaks, _ = measured_peaks()
