@@ -97,6 +97,17 @@ class Engine:
             self._job_start = torch.cuda.Event(enable_timing=True)
             self._job_start.record()
         while not self.finished:
+            if prefix_cache and pending:
+                # A preempted request waits at the head of the queue with its last sampled ids possibly still
+                # placeholders.  Admission hashes a prompt's full blocks into the prefix cache, so those ids
+                # must be real before the scheduler sees the request again.
+                for r in sch.waiting:
+                    if r.num_completion_tokens == 0:  # never started: everything behind it is fresh too
+                        break
+                    if unresolved[r.id]:
+                        while pending:
+                            resolve(pending.popleft())
+                        break
             batch = sch.schedule()
             if batch is None:
                 raise RuntimeError("nothing can be scheduled: a request needs more KV blocks than the pool holds")

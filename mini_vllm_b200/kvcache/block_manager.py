@@ -101,9 +101,14 @@ class KVCacheBlockManager:
         bs, n = self.block_size, len(req.tokens)
         toks = np.asarray(req.tokens, dtype="<i4")
         chain, missed = NO_HASH, False
+        # A negative id stands for a sampled token that has not reached the host yet (the pipelined engine's
+        # placeholder).  A block holding one is neither looked up nor published, and neither is any block
+        # behind it: its hash would chain over content that is not the request's.
+        unknown = np.flatnonzero(toks < 0)
+        first_unknown = int(unknown[0]) if unknown.size else n
         for start in range(0, n, bs):
             full = start + bs <= n
-            if not (full and self.support_prefix_cache):
+            if not (full and self.support_prefix_cache) or start + bs > first_unknown:
                 req.blocks.append(self._take())
                 continue
             content = toks[start:start + bs].tobytes()

@@ -150,3 +150,48 @@ def test_pipelined_loop_with_prefix_cache():
     # the pipelined run has published (almost) the same blocks: a request may lose its last full block when
     # it finishes before that block's tokens have arrived
     assert sum(piped_cached) >= 0.8 * sum(plain_cached)
+
+
+def test_prefix_cache_never_sees_placeholder_tokens():
+    """A preempted request goes back to the head of the queue while its last sampled ids may still be
+    placeholders on the host.  Whatever is published to the prefix cache, or counted as cached, must be
+    real tokens: identical prompts in a pool so tight that requests are preempted again and again."""
+    rnd = random.Random(5)
+    base = [rnd.randrange(1, 50) for _ in range(250)]
+    prompts = [list(base) for _ in range(8)] + [base + [rnd.randrange(1, 50) for _ in range(300)] for _ in range(4)]
+    params = [SamplingParams(max_tokens=rnd.randrange(270, 330), ignore_eos=True) for _ in prompts]
+
+    eng = make_engine(False, 9, prefix=True)
+    bm = eng.scheduler.block_manager
+    published, admitted = [], []
+    publish, allocate = bm._publish, bm.allocate_blocks_for_prefill
+
+    def spy_publish(bid, h, content):
+        published.append(np.frombuffer(content, dtype="<i4"))
+        return publish(bid, h, content)
+
+    def spy_allocate(req):
+        allocate(req)
+        admitted.append((req.num_cached_tokens, list(req.tokens[:req.num_cached_tokens])))
+
+    bm._publish, bm.allocate_blocks_for_prefill = spy_publish, spy_allocate
+    preempted = []
+    preempt = eng.scheduler.preempt
+    eng.scheduler.preempt = lambda r: (preempted.append(r.id), preempt(r))[1]
+    out = eng.generate(prompts, copy.deepcopy(params), use_tqdm=False)
+    assert [len(o["tokens"]) for o in out] == [sp.max_tokens for sp in params]
+    assert preempted, "the pool was not tight enough to preempt anybody"
+    assert published and all((c >= 0).all() for c in published), "a block with a placeholder was published"
+    assert all(min(toks, default=0) >= 0 for _, toks in admitted), "cached tokens cover a placeholder"
+    assert any(n > 0 for n, _ in admitted), "no prefix-cache hit happened"
+
+    # the block manager on its own: a prompt with an unknown id publishes nothing from that block on
+    from mini_vllm_b200.engine.request import Request
+    from mini_vllm_b200.kvcache.block_manager import KVCacheBlockManager
+    mgr = KVCacheBlockManager(8, 256, support_prefix_cache=True)
+    r = Request(list(range(1, 257)) + [5] * 255 + [-1] + [6] * 256 + [9])
+    mgr.allocate_blocks_for_prefill(r)
+    assert [mgr._hash[b] != -1 for b in r.blocks] == [True, False, False, False]
+    r2 = Request(list(r.tokens))
+    mgr.allocate_blocks_for_prefill(r2)
+    assert r2.num_cached_tokens == 256
