@@ -46,6 +46,16 @@ int mvb_abi_version(void);
 const char* mvb_status_string(int status);
 
 /*
+ * Self-test of the kernels' bounded waits.  (No counterpart in the reference.)
+ * Every wait inside the attention kernels is an mbarrier wait with an iteration limit; when it runs out
+ * the kernel records {4 = wait timeout, detail, block, thread} in dev_status and returns instead of
+ * hanging.  This entry runs that same wait, with `limit` polls (1..65536), on a barrier nothing arrives
+ * at, so the status path can be exercised without disturbing a real kernel: after the stream has drained
+ * dev_status[0] == 4 and dev_status[1] == limit.
+ */
+int mvb_selftest_wait_timeout(int32_t* dev_status, int limit, void* stream);
+
+/*
  * Prefill batch packing on the device.
  * Replaces Executor._build_prefill_input (minivllm/executor/executor.py:81-127) and
  * Executor._build_block_table (:156-163): from per-sequence facts it expands
@@ -197,7 +207,8 @@ int mvb_decode_attn_static(const void* q, int64_t q_row_stride, const void* k_ca
  *     through row s of the table (the prefix-cache case, attention.py:79-83).
  *   Query i of a sequence sits at position p = k_len - q_len + i and sees keys
  *   max(0, p - window_left) <= j <= p.
- * Supported: head_dim 128 (256 planned), any GQA ratio, block_size a multiple of 128.
+ * Supported: head_dim 128 or 256, any GQA ratio; with a block table, block_size a multiple of 128
+ * (head_dim 128) or of 64 (head_dim 256), the kernel's KV tile, so that a tile never straddles blocks.
  */
 int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void* k, int64_t k_row_stride, const void* v,
                      int64_t v_row_stride, int64_t kv_rows, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,

@@ -15,6 +15,7 @@ i32, i64, f32, u64, vp, sz = C.c_int, C.c_int64, C.c_float, C.c_uint64, C.c_void
 SIGNATURES = {
     "mvb_abi_version": (i32, []),
     "mvb_status_string": (C.c_char_p, [i32]),
+    "mvb_selftest_wait_timeout": (i32, [vp, i32, vp]),
     "mvb_pack_prefill": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]),
     "mvb_pack_decode": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, vp, vp, vp, vp, vp, vp, vp]),
     "mvb_rope_kv_write": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, i64, vp, vp, vp, i64, i32, i32, i32, i32, i32,

@@ -78,6 +78,7 @@ def _flatten_hf(cfg) -> SimpleNamespace:
             out.rope_theta = full["rope_theta"]
         if isinstance(local, dict) and "rope_theta" in local:
             out.rope_local_base_freq = local["rope_theta"]
+    out.sliding_window_counts_query = True      # checkpoints follow the Hugging Face window convention
     out.dtype = getattr(cfg, "dtype", None) or getattr(cfg, "torch_dtype", None) or torch.bfloat16
     if not hasattr(out, "head_dim"):
         out.head_dim = out.hidden_size // out.num_attention_heads

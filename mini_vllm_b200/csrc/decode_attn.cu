@@ -2,9 +2,15 @@
 //
 // Work unit: a "CTA tile" of CT tokens of one sequence, all KV heads of a head group.  A
 // one-CTA plan kernel (once per step; every layer reuses it) prefix-sums the tile counts and
-// hands each of the P persistent CTAs a contiguous range of tiles, so the load is balanced to
-// within one tile whatever the ragged lengths are, the grid never depends on data (CUDA-graph
-// capturable) and a sequence is split only where a CTA boundary falls inside it.
+// hands each of the P persistent CTAs a contiguous range of tiles, so the grid never depends on
+// data (CUDA-graph capturable).  Two ways of cutting the tile sequence are weighed per step:
+//   even     every CTA gets the same number of tiles (balanced to within one tile whatever the
+//            ragged lengths are); a sequence is split wherever a CTA boundary falls inside it and
+//            its parts are merged through global memory (see below);
+//   aligned  every boundary is moved to the nearest sequence boundary, so no sequence is split and
+//            nothing is merged.  Taken when its most loaded CTA has at most a few tiles more than
+//            the even cut gives everyone - the price of one merge - which is the case for many
+//            short contexts (a sliding-window layer, a batch of young requests).
 //
 // Inside a CTA every warp owns one KV head (and one 16-token sub-tile when there are more
 // warps than heads) and runs its own TMA -> shared-memory ring: the lane-0 thread issues
@@ -27,33 +33,16 @@
 #include "mini_vllm_b200.h"
 #include "scan.cuh"
 
-#include <mutex>
-
 namespace mvb {
-
-// Optional timeline probe (compiled in only with -DMVB_DECODE_TRACE): thread 0 of every CTA stamps
-// the SM clock at a few points so that fixed costs can be attributed.
-#ifdef MVB_DECODE_TRACE
-__device__ unsigned long long* g_decode_trace = nullptr;
-#define MVB_TRACE(i)                                                                          \
-  do {                                                                                        \
-    if (threadIdx.x == 0 && blockIdx.y == 0 && g_decode_trace != nullptr) {                   \
-      unsigned long long t_;                                                                  \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                   \
-      g_decode_trace[blockIdx.x * 16 + (i)] = t_;                                             \
-    }                                                                                         \
-  } while (0)
-#else
-#define MVB_TRACE(i)
-#endif
 
 constexpr int kMaxCtas = 160;          // workspace is sized for this many persistent CTAs
 constexpr int kPlanThreads = 256;
 constexpr int kMinTilesPerCta = 2;
 constexpr int kMaxPartsPerSeq = 32;   // target bound on the partials one sequence is split into
+constexpr int kMergeTiles = 4;        // what a partial + arrival + merge costs a CTA, in 64 KB tiles of streaming
 
 struct DecodeHeader {                  // first 32 bytes of the workspace (device memory)
-  int32_t total_tiles, per_cta, num_ctas, cta_tokens, num_seqs, window_left, pad0, pad1;
+  int32_t total_tiles, per_cta, num_ctas, cta_tokens, num_seqs, window_left, aligned, pad1;
 };
 
 // What a CTA needs to start streaming, written by the plan kernel so that the attention kernel
@@ -115,8 +104,8 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int32_t
                                                                    int64_t table_stride, int block_size,
                                                                    DecodeHeader* hdr, CtaDesc* descs,
                                                                    int32_t* tile_prefix) {
-  __shared__ int max_tiles_s;
-  if (threadIdx.x == 0) max_tiles_s = 0;
+  __shared__ int max_tiles_s, max_load_s;
+  if (threadIdx.x == 0) { max_tiles_s = 0; max_load_s = 0; }
   for (int i = threadIdx.x; i < num_counters; i += kPlanThreads) tile_prefix[num_seqs + 1 + i] = 0;
   __syncthreads();
   block_exclusive_scan<kPlanThreads>(
@@ -136,22 +125,40 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const int32_t
   // otherwise be cut into a hundred slivers whose merge costs more than the streaming)
   const int per_for_merge = (max_tiles_s + kMaxPartsPerSeq - 1) / kMaxPartsPerSeq;
   per = per < per_for_merge ? per_for_merge : per;
+  auto seq_of_tile = [&](int t) -> int {   // last b with tile_prefix[b] <= t (the sequence holding tile t < total)
+    int lo = 0, hi = num_seqs;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (tile_prefix[mid] <= t) lo = mid; else hi = mid;
+    }
+    return lo;
+  };
+  // the aligned cut: boundary c sits on the sequence boundary nearest to c * total / num_ctas
+  auto aligned_start = [&](int c) -> int {
+    if (c <= 0 || total == 0) return 0;
+    if (c >= num_ctas) return total;
+    const int ideal = static_cast<int>(static_cast<int64_t>(c) * total / num_ctas);
+    const int b = seq_of_tile(ideal);
+    const int below = tile_prefix[b], above = tile_prefix[b + 1];
+    return ideal - below <= above - ideal ? below : above;
+  };
+  for (int c = threadIdx.x; c < num_ctas; c += kPlanThreads)
+    atomicMax(&max_load_s, aligned_start(c + 1) - aligned_start(c));
+  __syncthreads();
+  const bool aligned = total > 0 && max_load_s <= per + kMergeTiles;
   if (threadIdx.x == 0) {
     hdr->total_tiles = total; hdr->per_cta = per; hdr->num_ctas = num_ctas; hdr->cta_tokens = cta_tokens;
-    hdr->num_seqs = num_seqs; hdr->window_left = window_left; hdr->pad0 = 0; hdr->pad1 = 0;
+    hdr->num_seqs = num_seqs; hdr->window_left = window_left; hdr->aligned = aligned ? 1 : 0; hdr->pad1 = 0;
   }
   for (int c = threadIdx.x; c < num_ctas; c += kPlanThreads) {
-    const int64_t t = static_cast<int64_t>(c) * per;
+    const int64_t even0 = static_cast<int64_t>(c) * per;
+    const int64_t t = aligned ? aligned_start(c) : even0;
     CtaDesc d;
     d.t0 = t < total ? static_cast<int32_t>(t) : total;
-    d.t1 = t + per < total ? static_cast<int32_t>(t + per) : total;
+    d.t1 = aligned ? aligned_start(c + 1) : (even0 + per < total ? static_cast<int32_t>(even0 + per) : total);
     d.b = num_seqs; d.tp0 = d.tp1 = d.n = 0; d.per = per; d.blk0 = -1;
-    if (t < total) {                   // last b with tile_prefix[b] <= t
-      int lo = 0, hi = num_seqs;
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (tile_prefix[mid] <= t) lo = mid; else hi = mid;
-      }
+    if (d.t0 < d.t1) {
+      const int lo = seq_of_tile(d.t0);
       d.b = lo; d.tp0 = tile_prefix[lo]; d.tp1 = tile_prefix[lo + 1]; d.n = cache_seqlens[lo];
       if (block_table != nullptr) {      // spare the attention kernel one dependent load before its first TMA
         const int start_al = visible_start(d.n, window_left) / cta_tokens * cta_tokens;
@@ -214,7 +221,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   const int kvh = blockIdx.y * HPC + head_local;
   const int G = p.group;
   const int c = blockIdx.x;
-  MVB_TRACE(0);
   CtaDesc desc;
   {
     const int4* dp = reinterpret_cast<const int4*>(p.descs + c);
@@ -233,7 +239,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       }
     }
   };
-  MVB_TRACE(1);
   if (t0 >= t1) {                                            // CTA-uniform: nothing to stream
     zero_empty_rows();
     return;
@@ -252,7 +257,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     for (int s = 0; s < NST; ++s) mbar_init(&bars[s], 1);
     fence_mbar_init();
   }
-  __syncthreads();
+  __syncwarp();                                              // a warp's barriers are armed and waited on by itself only
 
   // ---- producer side: the same tile walk as the consumer, NST-1 tiles ahead --------------------
   auto seq_from_desc = [&](SeqView& v) {
@@ -307,10 +312,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       return true;
     }
   };
-  MVB_TRACE(2);
 #pragma unroll
   for (int i = 0; i < NST - 1; ++i) fetch_next();
-  MVB_TRACE(3);
 
   // ---- consumer side ------------------------------------------------------------------------------
   SeqView cs;
@@ -354,7 +357,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
         dead = true;
         continue;
       }
-      if (ncomp == 0) MVB_TRACE(4);
       ++ncomp;
       const uint32_t kbase = my_stages + st * C::STAGE_BYTES;
       const uint32_t vbase = kbase + C::TILE_BYTES;
@@ -423,8 +425,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       }
       __syncwarp();
     }
-
-    MVB_TRACE(5);
     // ---- end of segment: merge the warps that share a head, then write output or partial --------
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
@@ -486,7 +486,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
         }
       }
     }
-    MVB_TRACE(6);
     if (!whole) {
       // combine pass without waiting: publish the partial, count the arrival; whoever arrives last
       // finds every partial of this sequence in memory and merges them
@@ -503,7 +502,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
         if (is_last) *cnt = 0;                               // re-arm for the next launch
       }
       __syncthreads();
-      MVB_TRACE(7);
       if (is_last) {
         constexpr int HEADS = HPC * 8;                       // upper bound of HPC * G
         constexpr int PC = 32;                               // partials weighted per pass
@@ -570,10 +568,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     }
     __syncthreads();
   }
-
-  MVB_TRACE(8);
   zero_empty_rows();
-  MVB_TRACE(9);
 
   // a wait that gave up may leave copies in flight: give them a bounded chance to land
   if (dead) {
@@ -589,29 +584,14 @@ static int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, const Dec
                       C::NW * C::NSTAGES * sizeof(uint64_t) +
                       static_cast<size_t>(C::NW) * p.group * C::FIN_STRIDE * sizeof(float);
   if (smem + 64 > 227 * 1024) return kUnsupportedShape;       // static shared memory counts too
-  static size_t configured_by_device[64] = {};                // opt in to > 48 KB once per device and size
-  int dev = 0;
-  cudaGetDevice(&dev);
-  size_t& configured = configured_by_device[dev & 63];
-  if (smem > configured) {
-    if (cudaFuncSetAttribute(decode_attn_kernel<D, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-      return kLaunchFailed;
-    configured = smem;
-  }
+  const int rc = opt_in_dynamic_smem<C>(reinterpret_cast<const void*>(&decode_attn_kernel<D, HPC>), smem);
+  if (rc != kOk) return rc;
   dim3 grid(num_ctas, hkv / HPC);
   decode_attn_kernel<D, HPC><<<grid, C::NW * 32, smem, stream>>>(km, vm, p);
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
 }  // namespace mvb
-
-#ifdef MVB_DECODE_TRACE
-extern "C" int mvb_debug_set_decode_trace(void* ptr) {
-  unsigned long long* p = static_cast<unsigned long long*>(ptr);
-  return cudaMemcpyToSymbol(mvb::g_decode_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 extern "C" size_t mvb_decode_workspace_bytes(int max_seqs, int num_q_heads, int head_dim) {
   if (max_seqs <= 0 || num_q_heads <= 0 || head_dim <= 0) return 0;
@@ -626,6 +606,24 @@ static int decode_shape_ok(int hq, int hkv, int d) {
   const int nw = d == 128 ? 8 : 4;
   if (hkv < nw) return (hkv == 1 || hkv == 2 || hkv == 4);
   return hkv % nw == 0;
+}
+
+// Everything about a decode-attention call that can be rejected before anything is enqueued.
+static int decode_check_args(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                             int64_t num_blocks, int block_size, const int32_t* cache_seqlens,
+                             const int32_t* block_table, int64_t table_stride, int table_width, int num_seqs,
+                             int num_q_heads, int num_kv_heads, int head_dim, const void* out,
+                             int64_t out_row_stride) {
+  using namespace mvb;
+  if (!q || !k_cache || !v_cache || !cache_seqlens || !block_table || !out) return kInvalidArgument;
+  if (num_seqs <= 0 || num_blocks <= 0 || block_size <= 0 || table_width <= 0 || table_stride < table_width)
+    return kInvalidArgument;
+  if (!decode_shape_ok(num_q_heads, num_kv_heads, head_dim)) return kUnsupportedShape;
+  if (block_size % 16 != 0) return kUnsupportedShape;
+  if (num_blocks * block_size > 0x7fffffffLL) return kUnsupportedShape;
+  if ((q_row_stride % 2) || (out_row_stride % 4) || !is_aligned(q, 4) || !is_aligned(out, 8)) return kMisaligned;
+  if (!is_aligned(k_cache, 16) || !is_aligned(v_cache, 16)) return kMisaligned;
+  return kOk;
 }
 
 static int decode_plan_impl(const int32_t* cache_seqlens, const int32_t* block_table, int64_t table_stride,
@@ -669,19 +667,17 @@ extern "C" int mvb_decode_attn(const void* q, int64_t q_row_stride, const void* 
                                void* out, int64_t out_row_stride, void* workspace, size_t workspace_bytes,
                                int32_t* dev_status, void* stream) {
   using namespace mvb;
-  if (!q || !k_cache || !v_cache || !cache_seqlens || !block_table || !out || !workspace) return kInvalidArgument;
-  if (num_seqs <= 0 || num_blocks <= 0 || block_size <= 0 || table_width <= 0 || table_stride < table_width)
-    return kInvalidArgument;
-  if (!decode_shape_ok(num_q_heads, num_kv_heads, head_dim)) return kUnsupportedShape;
-  if (block_size % 16 != 0) return kUnsupportedShape;
-  if (num_blocks * block_size > 0x7fffffffLL) return kUnsupportedShape;
-  if ((q_row_stride % 2) || (out_row_stride % 4) || !is_aligned(q, 4) || !is_aligned(out, 8)) return kMisaligned;
+  if (!workspace) return kInvalidArgument;
+  int rc = decode_check_args(q, q_row_stride, k_cache, v_cache, num_blocks, block_size, cache_seqlens, block_table,
+                             table_stride, table_width, num_seqs, num_q_heads, num_kv_heads, head_dim, out,
+                             out_row_stride);
+  if (rc != kOk) return rc;
   const DecodeLayout l = decode_layout(num_seqs, num_q_heads, head_dim);
   if (workspace_bytes < l.total || !is_aligned(workspace, 256)) return kInvalidArgument;
 
   CUtensorMap km, vm;
   const int64_t rows = num_blocks * block_size;
-  int rc = make_kv_tensor_map(&km, k_cache, rows, num_kv_heads, head_dim, static_cast<int64_t>(num_kv_heads) * head_dim, 16);
+  rc = make_kv_tensor_map(&km, k_cache, rows, num_kv_heads, head_dim, static_cast<int64_t>(num_kv_heads) * head_dim, 16);
   if (rc != kOk) return rc;
   rc = make_kv_tensor_map(&vm, v_cache, rows, num_kv_heads, head_dim, static_cast<int64_t>(num_kv_heads) * head_dim, 16);
   if (rc != kOk) return rc;
@@ -739,9 +735,9 @@ static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticSc
 // memory, which differs per device.  Looked up once per device, with that device current.
 static int static_scratch_address(void** out) {
   static std::mutex mu;
-  static void* addr_by_device[64] = {};
+  static void* addr_by_device[kMaxDevices] = {};
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kLaunchFailed;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return kLaunchFailed;
   std::lock_guard<std::mutex> lock(mu);
   if (addr_by_device[dev] == nullptr) {
     void* ptr = nullptr;
@@ -761,11 +757,15 @@ extern "C" int mvb_decode_attn_static(const void* q, int64_t q_row_stride, const
                                       int window_left, void* out, int64_t out_row_stride, int32_t* dev_status,
                                       void* stream) {
   using namespace mvb;
-  if (num_seqs <= 0 || num_q_heads <= 0 || head_dim <= 0) return kInvalidArgument;
-  if (!decode_shape_ok(num_q_heads, num_kv_heads, head_dim)) return kUnsupportedShape;
+  // every argument is checked before the plan kernel goes out: a negative return means nothing was enqueued
+  int rc = decode_check_args(q, q_row_stride, k_cache, v_cache, num_blocks, block_size, cache_seqlens, block_table,
+                             table_stride, table_width, num_seqs, num_q_heads, num_kv_heads, head_dim, out,
+                             out_row_stride);
+  if (rc != kOk) return rc;
   if (decode_layout(num_seqs, num_q_heads, head_dim).total > kStaticScratchBytes) return kScratchTooSmall;
+  if (encode_tiled_fn() == nullptr) return kNoDriverEntry;
   void* scratch = nullptr;
-  int rc = static_scratch_address(&scratch);
+  rc = static_scratch_address(&scratch);
   if (rc != kOk) return rc;
   // The plan launch rewrites the descriptors and zeroes the arrival counters, so nothing left in
   // the array by an earlier call is read.

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mvb {
@@ -47,14 +49,39 @@ inline int make_kv_tensor_map(CUtensorMap* map, const void* base, int64_t rows, 
   return r == CUDA_SUCCESS ? kOk : kTensorMapFailed;
 }
 
+// Per-device facts are looked up once per device, under a lock, so that the first calls of two threads
+// (or calls on two different GPUs of one process) cannot see each other's half-written state.
+constexpr int kMaxDevices = 64;
+
 inline int sm_count() {
-  static int n = []() {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
-    return v;
-  }();
-  return n;
+  static std::mutex mu;
+  static int by_device[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  std::lock_guard<std::mutex> lock(mu);
+  if (by_device[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    by_device[dev] = v;
+  }
+  return by_device[dev];
+}
+
+// Opts a kernel in to `bytes` of dynamic shared memory (beyond the 48 KB default) once per device and
+// size.  Tag names the kernel instantiation: each one keeps its own table.
+template <class Tag>
+inline int opt_in_dynamic_smem(const void* kernel, size_t bytes) {
+  static std::mutex mu;
+  static size_t configured[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return kLaunchFailed;
+  std::lock_guard<std::mutex> lock(mu);
+  if (bytes > configured[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
+      return kLaunchFailed;
+    configured[dev] = bytes;
+  }
+  return kOk;
 }
 
 }  // namespace mvb

@@ -36,23 +36,6 @@
 
 namespace mvb {
 
-// Optional event log (only with -DMVB_PREFILL_EVLOG): the CTA that starts on block (0,0,0) appends
-// (code, SM clock) pairs per role to a caller-provided buffer of 4 x 512 words.
-#ifdef MVB_PREFILL_EVLOG
-__device__ unsigned long long* g_prefill_evlog = nullptr;
-#define MVB_EV_DECL(role, on) int ev_n_ = 0; const int ev_role_ = (role); \
-  const bool ev_on_ = (on) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && g_prefill_evlog != nullptr;
-#define MVB_EV(code)                                                                               \
-  do {                                                                                             \
-    if (ev_on_ && ev_n_ < 512)                                                                     \
-      g_prefill_evlog[ev_role_ * 512 + ev_n_++] =                                                  \
-          (static_cast<unsigned long long>(code) << 48) | (static_cast<unsigned long long>(clock64()) & 0xffffffffffffULL); \
-  } while (0)
-#else
-#define MVB_EV_DECL(role, on)
-#define MVB_EV(code)
-#endif
-
 struct PrefillParams {
   const int32_t* cu_q;
   const int32_t* cu_k;
@@ -226,7 +209,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     uint32_t k_issued = 0, v_issued = 0;                      // lane 0: K / V tile loads handed to TMA
     bool clc_pending = false;                                 // lane 0: a request whose response has not been read
     bool ok = true, have = true;
-    MVB_EV_DECL(0, lane == 0)
     if (lane == 0) { tma_prefetch_desc(&q_map); tma_prefetch_desc(&k_map); tma_prefetch_desc(&v_map); }
     auto publish = [&](int x, int y, int z, int valid) {      // lane 0
       const int slot = n_pub & 1;
@@ -257,12 +239,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       return blk * p.block_size + tok % p.block_size;
     };
     while (ok && have) {
-      MVB_EV(10);
       item.init(p, bx, by, bz);
-      MVB_EV(item.empty ? 19 : 11);
       if (lane == 0) {
         if (!item.empty) publish(bx, by, bz, 1);
-        MVB_EV(12);
         if (ok) {                                             // ask for the next index while this one is worked on
           fence_proxy_async();                                // the response slot was last read with ordinary loads
           mbar_arrive_expect_tx(&bars[B_CLC], 16);
@@ -275,7 +254,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         // They are asked for after the item's first K and V tiles, which do not have to wait for that.
         auto load_q = [&]() {                                 // lane 0
           if (n_pub >= 2) ok = wait(B_QFREE, n_pub & 1, 920);
-          MVB_EV(13);
 #pragma unroll
           for (int t = 0; t < NQ; ++t) {
             if (!ok || item.rows[t] <= 0) continue;
@@ -299,10 +277,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             const int z = kv_row(j);
             if (g >= 2) ok = wait(B_KFREE + st, ring_parity ^ 1, 100);
             if (ok) { load_tile(&k_map, k_s + st * C::KV_BYTES, &bars[B_KFULL + st], z); ++k_issued; }
-            MVB_EV(15);
             if (ok && g >= 2) ok = wait(B_VFREE + st, ring_parity ^ 1, 200);
             if (ok) { load_tile(&v_map, v_s + st * C::KV_BYTES, &bars[B_VFULL + st], z); ++v_issued; }
-            MVB_EV(16);
             if (ok && it == 0) load_q();
           }
           ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -328,9 +304,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       // the next index (or the end of the work)
       int nx = 0, ny = 0, nz = 0, more = 0;
       if (lane == 0 && ok) {
-        MVB_EV(17);
         ok = wait(B_CLC, n_clc & 1, 930);
-        MVB_EV(18);
         if (ok) {
           clc_pending = false;
           more = clc_query(clc_resp, nx, ny, nz) ? 1 : 0;
@@ -485,10 +459,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     uint32_t n_s = 0, n_epi = 0;                              // S tiles consumed (S / P parity), epilogues done (O parity)
     bool ok = true;
     Item item;
-    MVB_EV_DECL(2 + t, row == 0)
-    MVB_EV(30);
     for (uint32_t n_item = 0; ok && next_item(n_item, item); ++n_item) {
-      MVB_EV(31);
       // this group's tile, picked with selects so the item stays in registers
       int rows_me = item.rows[0], pf_me = item.pf[0], pl_me = item.pl[0], jlo_me = item.jlo[0], jhi_me = item.jhi[0],
           roff_me = item.roff[0], head_me = item.head[0];
@@ -509,7 +480,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         ok = wait(B_SFULL + t, n_s & 1, 700);
         if (!ok) break;
         tc_fence_after();
-        MVB_EV(32);
         // Visible keys of this row inside the tile: [vis_lo, vis_hi] relative to col0.  The rows of a
         // warp are consecutive, so a 32-key chunk is classified once per warp: visible to all 32 rows
         // (no mask arithmetic), to none (not loaded at all; P = 0), or mixed (per-element mask bits).
@@ -569,7 +539,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 #pragma unroll
           for (int c = 0; c < NCH; ++c) tmem_ld_32x32(s_addr + c * 32, sreg[c]);
           tmem_wait_ld();
-          MVB_EV(36);
           float max0 = -INFINITY, max1 = -INFINITY;
 #pragma unroll
           for (int c = 0; c < NCH; ++c)
@@ -578,10 +547,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
               max0 = fmax3(max0, __uint_as_float(sreg[c][i]), __uint_as_float(sreg[c][i + 1]));
               max1 = fmax3(max1, __uint_as_float(sreg[c][i + 2]), __uint_as_float(sreg[c][i + 3]));
             }
-          MVB_EV(37);
           new_max(fmaxf(max0, max1));
           const float m_safe = m_use == -INFINITY ? 0.f : m_use;
-          MVB_EV(38);
 #pragma unroll
           for (int c = 0; c < NCH; ++c) {
             uint32_t pk[16];
@@ -593,7 +560,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
               pk[i >> 1] = pack_bf16(e0, e1);
             }
             publish_p(c, pk);
-            if (c == 1) MVB_EV(39);
           }
         } else {
           // chunks every row of the warp sees completely run the plain code here too
@@ -652,12 +618,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         }
         l_run = l_run * alpha + (sum0 + sum1);
         m_run = m_use;
-        MVB_EV(33);
       }
       // ---- epilogue: while it runs, the other roles are already at work on the next item ------------
       if (ok) ok = wait(B_ODONE + t, n_epi & 1, 800);
       ++n_epi;
-      MVB_EV(34);
       if (ok) {
         tc_fence_after();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -676,7 +640,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           tc_fence_before();
           mbar_arrive(&bars[B_OFREE + t]);
         }
-        MVB_EV(35);
         // A thread owns a row, so storing from registers would touch 32 lines per instruction.  Each
         // warp turns its 32 rows through a 4 KB staging tile (16-byte units XOR-swizzled by the row,
         // conflict-free both ways) and writes whole 128-byte lines, 64 columns at a time.
@@ -703,7 +666,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           }
           __syncwarp();
         }
-        MVB_EV(36);
       }
     }
   }
@@ -730,15 +692,8 @@ static int launch_prefill(const PrefillOperands& op, const PrefillParams& p, int
   if (rc != kOk) return rc;
   rc = make_kv_tensor_map(&vm, op.v, op.kv_rows, op.hkv, D, op.v_stride, BN);
   if (rc != kOk) return rc;
-  static bool configured_by_device[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!configured_by_device[dev & 63]) {
-    if (cudaFuncSetAttribute(prefill_attn_kernel<D, BN, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) !=
-        cudaSuccess)
-      return kLaunchFailed;
-    configured_by_device[dev & 63] = true;
-  }
+  rc = opt_in_dynamic_smem<C>(reinterpret_cast<const void*>(&prefill_attn_kernel<D, BN, NQ>), C::SMEM);
+  if (rc != kOk) return rc;
   PrefillParams pp = p;
   pp.pair_heads = (NQ > 1 && p.group % NQ == 0) ? 1 : 0;
   const int rows_per_cta = pp.pair_heads ? 128 : 128 * NQ;
@@ -749,13 +704,6 @@ static int launch_prefill(const PrefillOperands& op, const PrefillParams& p, int
 }
 
 }  // namespace mvb
-
-#ifdef MVB_PREFILL_EVLOG
-extern "C" int mvb_debug_set_prefill_evlog(void* ptr) {
-  unsigned long long* p = static_cast<unsigned long long*>(ptr);
-  return cudaMemcpyToSymbol(mvb::g_prefill_evlog, &p, sizeof(p)) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 extern "C" int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void* k, int64_t k_row_stride,
                                 const void* v, int64_t v_row_stride, int64_t kv_rows,

@@ -121,11 +121,16 @@ class DecoderLM(nn.Module):
         self.rotary = RotaryEmbedding(cfg.head_dim, cfg.max_position_embeddings, cfg.rope_theta)
         self.rotary_local = (RotaryEmbedding(cfg.head_dim, cfg.max_position_embeddings, cfg.rope_local_base_freq)
                              if gemma else None)
+        # The reference hands its attention layer (sliding_window, -1) and that layer's contract reads the
+        # first number as "tokens to the left of the query" (gemma3.py:66-69, attention.py:56-60): a query
+        # then sees sliding_window + 1 keys.  Hugging Face counts the query itself in the window
+        # (sliding_window keys); configs read from a checkpoint ask for that with sliding_window_counts_query.
+        left = (cfg.sliding_window - (1 if getattr(cfg, "sliding_window_counts_query", False) else 0)) if gemma else -1
         layers = []
         for i in range(cfg.num_hidden_layers):
             local = gemma and (i + 1) % 6 != 0
             layers.append(DecoderLayer(cfg, self.rotary_local if local else self.rotary, gemma,
-                                       (cfg.sliding_window, -1) if local else (-1, -1)))
+                                       (left, -1) if local else (-1, -1)))
         self.layers = nn.ModuleList(layers)
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, gemma)
         self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)

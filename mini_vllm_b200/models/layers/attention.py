@@ -19,10 +19,13 @@ from ... import ops
 from ...executor.context import Context
 
 _workspaces: dict = {}
+_superseded: list = []      # outgrown buffers stay allocated: captured CUDA graphs keep writing through their pointers
 
 
 def _decode_workspace(device, max_seqs: int, num_heads: int, head_dim: int, window_left: int) -> torch.Tensor:
-    """One scratch buffer per (device, head shape, window); grown when a larger batch arrives."""
+    """One scratch buffer per (device, head shape, window); a larger one takes its place when a larger batch
+    arrives.  The smaller buffer is never freed: a graph captured while it was current has its address
+    baked in, and a replay after the memory went back to the allocator would scribble over someone else."""
     key = (device, num_heads, head_dim, window_left)
     ws = _workspaces.get(key)
     need = ops._cabi.load().mvb_decode_workspace_bytes(max_seqs, num_heads, head_dim)
@@ -30,6 +33,8 @@ def _decode_workspace(device, max_seqs: int, num_heads: int, head_dim: int, wind
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError("decode workspace must be allocated before CUDA graph capture "
                                "(run one eager decode step of the largest batch first)")
+        if ws is not None:
+            _superseded.append(ws)
         ws = ops.decode_workspace(max(max_seqs, 512), num_heads, head_dim, device)
         _workspaces[key] = ws
     return ws

@@ -56,6 +56,14 @@ def check_status(status: torch.Tensor) -> None:
                                 f"block {block}, thread {thread}")
 
 
+def selftest_wait_timeout(status: torch.Tensor, limit: int = 1024) -> None:
+    """Run the kernels' bounded mbarrier wait on a barrier nobody arrives at; ``status`` then reads
+    ``[4, limit, 0, 0]`` (a wait timeout), and the stream carries on."""
+    _need(status, torch.int32, "status")
+    _cabi.check(_cabi.load().mvb_selftest_wait_timeout(_ptr(status), int(limit), _stream()), "mvb_selftest_wait_timeout")
+    LaunchCounter.add(1)
+
+
 def pack_prefill(meta: torch.Tensor, num_seqs: int, num_tokens: int, num_blocks_total: int, table_width: int,
                  block_size: int, want_table: bool, status: torch.Tensor | None = None) -> dict:
     """meta: device int32 = [seq_len(B) | cached_len(B) | blk_off(B+1) | blocks_flat | new_tokens(T)]."""

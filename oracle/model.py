@@ -53,7 +53,11 @@ class OracleModel:
         q, k = norm(q, w[p + "q_norm.weight"], cfg.rms_norm_eps), norm(k, w[p + "k_norm.weight"], cfg.rms_norm_eps)
         local = self.gemma and (i + 1) % 6 != 0                         # gemma3.py:210-211
         q, k = rope_kv.apply_rope(positions, q, k, self.table_local if local else self.table)
-        window = cfg.sliding_window if (local and self.use_window) else -1
+        # (sliding_window, -1) at gemma3.py:66-69 = that many keys to the left of the query; a config that
+        # sets sliding_window_counts_query asks for the Hugging Face convention (the query is one of them)
+        window = -1
+        if local and self.use_window:
+            window = cfg.sliding_window - (1 if getattr(cfg, "sliding_window_counts_query", False) else 0)
         scale = (cfg.query_pre_attn_scalar if self.gemma else d) ** -0.5
         kc, vc = self.k_cache[i], self.v_cache[i]
         if ctx["slot_mapping"] is not None and ctx["slot_mapping"].numel() == k.shape[0]:

@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol_and_binding_covers_them():
 
 def test_host_only_calls_work_without_a_gpu():
     lib = _cabi.load()
-    assert lib.mvb_abi_version() == 3
+    assert lib.mvb_abi_version() >= 4
     assert lib.mvb_status_string(0) == b"ok"
     assert b"scratch" in lib.mvb_status_string(-7)
     assert lib.mvb_decode_workspace_bytes(512, 16, 128) > 2 * 160 * 16 * 128 * 4
@@ -42,6 +42,10 @@ def test_host_only_calls_work_without_a_gpu():
                                  None, None) == -2          # head_dim not a multiple of 16
     assert lib.mvb_sample(None, 0, 1, 10, None, None, None, 0, 0, None, None, None, None, None) == -1
     assert lib.mvb_decode_plan(None, 1, -1, 16, 8, 128, None, 0, None) == -1
+    assert lib.mvb_selftest_wait_timeout(None, 16, None) == -1
+    # the scratch-free decode entry looks at every operand before its first launch
+    assert lib.mvb_decode_attn_static(None, 0, None, None, 1, 256, None, None, 1, 1, 1, 16, 8, 128, 1.0, -1, None, 0,
+                                      None, None) == -1
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -132,3 +132,33 @@ def test_bad_block_id_is_reported_not_fatal(cuda):
     ops.decode_attn(q, k_pool.to(cuda), v_pool.to(cuda), seqlens, bt, d ** -0.5, -1, ws, status=status)
     torch.cuda.synchronize()
     assert status[0].item() == 2
+
+
+def plan_header(ws: torch.Tensor) -> dict:
+    names = ["total_tiles", "per_cta", "num_ctas", "cta_tokens", "num_seqs", "window_left", "aligned"]
+    return dict(zip(names, ws[:28].view(torch.int32).tolist()))
+
+
+def planned(cuda, lens, hq, hkv, d, window_left):
+    ws = ops.decode_workspace(len(lens), hq, d, cuda)
+    ops.decode_plan(torch.tensor(lens, dtype=torch.int32, device=cuda), window_left, hq, hkv, d, ws)
+    torch.cuda.synchronize()
+    return plan_header(ws)
+
+
+def test_plan_keeps_short_sequences_whole(cuda):
+    """Many short contexts: every CTA boundary sits on a sequence boundary (nothing to merge).  A few long
+    contexts: the even cut, with sequences split across CTAs.  Both give the oracle's result."""
+    g = generator(41)
+    short = [int(x) for x in torch.randint(290, 311, (140,), generator=g)]     # 19-20 tiles each, 19 per CTA if cut evenly
+    hdr = planned(cuda, short, 16, 8, 128, -1)
+    assert hdr["aligned"] == 1 and hdr["num_seqs"] == 140 and hdr["cta_tokens"] == 16
+    run_case(cuda, short, 16, 8, 128, seed=42)
+    windowed = [int(x) for x in torch.randint(512, 4096, (128,), generator=g)]
+    assert planned(cuda, windowed, 4, 1, 256, 512)["aligned"] == 1        # a sliding-window layer of config 4
+    assert planned(cuda, windowed, 4, 1, 256, -1)["aligned"] == 0         # its global layer
+    run_case(cuda, windowed, 4, 1, 256, window_left=512, seed=43)
+    assert planned(cuda, [9000, 40, 2000], 16, 8, 128, -1)["aligned"] == 0
+    assert planned(cuda, [0, 0, 0], 16, 8, 128, -1)["total_tiles"] == 0
+    # sequences of zero length between the others do not upset the boundaries
+    run_case(cuda, [300, 0, 0, 280, 310, 0, 295] * 12, 16, 8, 128, seed=44)

@@ -68,8 +68,14 @@ def check_tokens(engine, family, prompts, params, cfg, got):
     return exact, steps
 
 
+def small_gemma3_hf_window(**kw):
+    """The same model with the Hugging Face window convention (the query counts as one of the 64 keys)."""
+    return small_gemma3(sliding_window_counts_query=True, **kw)
+
+
 @pytest.mark.parametrize("family,shape,graphs", [("qwen3", small_qwen3, True), ("qwen3", small_qwen3, False),
-                                                  ("gemma3", small_gemma3, True)])
+                                                  ("gemma3", small_gemma3, True),
+                                                  ("gemma3", small_gemma3_hf_window, True)])
 def test_greedy_tokens_match_oracle(cuda, family, shape, graphs):
     g = generator(5)
     lens = randint(g, 5, 700, 12)
