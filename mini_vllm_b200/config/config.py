@@ -40,6 +40,10 @@ class Config:
     use_cuda_graph: bool = True
     max_graph_batch_size: int = 256          # largest decode batch replayed from a CUDA graph (graph.py:11)
     seed: int = 0                            # weights of a random-init model and the sampler's stream
+    # True: per-head q/k RMSNorm, RoPE and the cache write run as one kernel (results within one bf16 ulp of the
+    # unfused sequence).  False: stand-alone norms, then the RoPE + write kernel whose cache contents are
+    # bit-identical to the reference's eager rotation and copy.
+    fuse_qk_norm: bool = True
 
     def __post_init__(self):
         if self.hf_config is None:

@@ -55,10 +55,16 @@ class Attention(nn.Module):
         self.q_norm = RMSNorm(self.d, cfg.rms_norm_eps, gemma)
         self.k_norm = RMSNorm(self.d, cfg.rms_norm_eps, gemma)
         self.attn = FlashAttention(self.hq, self.d, scaling, self.hkv, sliding_window)
+        self.fuse_qk_norm = True                                 # Config.fuse_qk_norm, set by the loader
 
     def forward(self, ctx: Context, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         q, k, v = self.qkv_proj(x).split([self.q_dim, self.kv_dim, self.kv_dim], dim=-1)
         q, k, v = q.view(-1, self.hq, self.d), k.view(-1, self.hkv, self.d), v.view(-1, self.hkv, self.d)
+        if not self.fuse_qk_norm:
+            # the reference's sequence (qwen3.py:89-94): stand-alone per-head norms, then RoPE + cache write in
+            # the kernel whose cache contents are bit-identical to the eager rotation and copy
+            o = self.attn.forward_fused(ctx, self.q_norm(q), self.k_norm(k), v, positions, self.rotary.cos_sin_cache)
+            return self.o_proj(o.reshape(-1, self.q_dim))
         # per-head norms, RoPE and the KV write run as one kernel on the packed projection output
         o = self.attn.forward_fused_norm(ctx, q, k, v, positions, self.rotary.cos_sin_cache, self.q_norm.weight,
                                          self.k_norm.weight, self.q_norm.eps, self.q_norm.unit_offset)

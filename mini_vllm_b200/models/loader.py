@@ -32,6 +32,10 @@ def load_model(config, device="cuda") -> torch.nn.Module:
     finally:
         torch.set_default_dtype(prev)
     model.to(device)          # moves the CPU-built fp32 cos/sin tables; parameters are already there
+    fuse = bool(getattr(config, "fuse_qk_norm", True))
+    for module in model.modules():
+        if hasattr(module, "fuse_qk_norm"):
+            module.fuse_qk_norm = fuse
     if config.model is not None:
         model.load_weights(_weights(os.path.expanduser(config.model)))
     else:
