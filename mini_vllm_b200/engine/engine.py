@@ -178,3 +178,6 @@ class Engine:
         dec = self.tokenizer.decode if self.tokenizer is not None else (lambda toks: None)
         return [{"prompt": dec(r.prompt_tokens), "completion": dec(r.completion_tokens),
                  "tokens": r.completion_tokens} for r in done]
+
+
+LLM = Engine      # the name offline-inference scripts use for this class

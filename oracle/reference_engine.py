@@ -56,10 +56,13 @@ class ReferenceEngine:
     """``generate(prompts, max_tokens)`` through the reference's scheduler, executor and model on ``device``."""
 
     def __init__(self, hf_config, weights: dict, device, kv_cache_num_blocks: int = 256, max_num_batched_seqs: int = 64,
-                 max_num_batched_tokens: int = 16384, kv_cache_block_size: int = 256):
+                 max_num_batched_tokens: int = 16384, kv_cache_block_size: int = 256, attention_functions=None):
+        """``attention_functions``: ``(flash_attn_varlen_func, flash_attn_with_kvcache)`` to put where the
+        reference's attention layer looks its two functions up; default: the fp32 gather-and-SDPA stand-in."""
         if not available():
             raise RuntimeError("the reference package has not been staged (python -m oracle.stage_reference)")
         _install_stubs()
+        self.attention_functions = attention_functions
         import minivllm.executor.executor as ref_executor
         from minivllm.models.models import get_model_class
         from minivllm.scheduler.scheduler import Scheduler
@@ -138,6 +141,10 @@ class ReferenceEngine:
             return plain_sample(logits, batch)
 
         ex.sample = recording_sample
+        import minivllm.models.layers.attention as ref_attention
+        bound = (ref_attention.flash_attn_varlen_func, ref_attention.flash_attn_with_kvcache)
+        if self.attention_functions is not None:      # the names the layer resolves at call time (attention.py:84-91)
+            ref_attention.flash_attn_varlen_func, ref_attention.flash_attn_with_kvcache = self.attention_functions
         default_device, default_dtype = torch.get_default_device(), torch.get_default_dtype()
         torch.set_default_device(self.device)
         torch.set_default_dtype(self.config.hf_config.dtype)
@@ -157,6 +164,7 @@ class ReferenceEngine:
                     sch.update(batch, tokens)
         finally:
             ex.sample = plain_sample
+            ref_attention.flash_attn_varlen_func, ref_attention.flash_attn_with_kvcache = bound
             torch.tensor, torch.Tensor.cuda = plain_tensor, plain_cuda
             torch.set_default_device(default_device)
             torch.set_default_dtype(default_dtype)
