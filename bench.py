@@ -43,7 +43,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 from mini_vllm_b200.config import Config, SamplingParams, qwen3_shape  # noqa: E402
-from mini_vllm_b200.dispatcher import partition_by_tokens  # noqa: E402
+from mini_vllm_b200.dispatcher import partition_by_tokens, request_cost  # noqa: E402
 from mini_vllm_b200.workloads import (GEMMA3_1B, QWEN3_0P6B, config2_requests, config3, config4,  # noqa: E402
                                        decode_kv_bytes, prefill_flops)
 
@@ -63,7 +63,7 @@ def workload_requests(workload: str, world: int = 1, rank: int = 0):
     0.01 % but leaves the replicas' attention work 3 % apart, and a job is bound by its slowest replica.)
     Config 5 is 4096 requests over 8 GPUs: it is cut into its 8 shares once, and a run on N GPUs takes the
     first N of them, so every replica's job is the same at every N."""
-    kv_tokens = lambda r: r.max_tokens * (2 * len(r.prompt) + r.max_tokens) // 2
+    kv_tokens = lambda r: request_cost(len(r.prompt), r.max_tokens)
     if workload == "config5" and world <= 8:
         from mini_vllm_b200.workloads import config5_requests
         all_reqs, parts = config5_requests(seed=0, n=4096), 8
@@ -136,35 +136,54 @@ def build_engine(local_rank: int, workload: str = "config5", mixed_steps: bool =
     return Engine(dataclasses.replace(build_config(workload), enable_mixed_steps=mixed_steps))
 
 
-def run_job(engine, reqs, record_contexts=None):
-    """One generation job through the public API; returns (tokens processed, wall seconds, cuda ms)."""
-    prompts = [r.prompt for r in reqs]
-    params = [SamplingParams(max_tokens=r.max_tokens, ignore_eos=True) for r in reqs]
-    ex = engine.executor
-    if record_contexts is not None:
-        orig = ex.launch
-        count = [0]
+class ContextSpy:
+    """Records the contexts of every 40th decode step of a job (for the in-situ roofline replay)."""
 
-        def spy(batch, slots):
-            if batch.type == 1:
-                if count[0] % 40 == 20:
-                    record_contexts.append(([len(r.tokens) for r in batch.requests],
-                                            [list(r.blocks) for r in batch.requests]))
-                count[0] += 1
-            return orig(batch, slots)
-        ex.launch = spy
+    def __init__(self, executor, sink):
+        self.ex, self.sink, self.count, self.orig = executor, sink, 0, executor.launch
+
+    def __enter__(self):
+        if self.sink is not None:
+            def spy(batch, slots):
+                if batch.type == 1:
+                    if self.count % 40 == 20:
+                        self.sink.append(([len(r.tokens) for r in batch.requests], [list(r.blocks) for r in batch.requests]))
+                    self.count += 1
+                return self.orig(batch, slots)
+            self.ex.launch = spy
+        return self
+
+    def __exit__(self, *exc):
+        self.ex.launch = self.orig
+        return False
+
+
+def run_job(engine, reqs, record_contexts=None, group=None):
+    """One generation job through the public API; returns (tokens processed, wall seconds, this rank's cuda ms).
+
+    ``group is None``: this process's ``Engine.generate`` on ``reqs``.  Otherwise a collective over the ranks of
+    ``group``: rank 0 holds ``reqs`` (ALL requests of the job), the host dispatcher scatters the shares, every rank
+    generates, rank 0 gathers and merges; the wall time on rank 0 covers all of it and the token count is taken from
+    the merged results (other ranks return 0 tokens).
+    """
+    prompts = params = None
+    if reqs is not None:
+        prompts = [r.prompt for r in reqs]
+        params = [SamplingParams(max_tokens=r.max_tokens, ignore_eos=True) for r in reqs]
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
-    e0.record()
-    out = engine.generate(prompts, params, use_tqdm=False)
-    e1.record()
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
-    if record_contexts is not None:
-        ex.launch = orig
-    n_tok = sum(len(p) for p in prompts) + sum(len(o["tokens"]) for o in out)
-    assert all(len(o["tokens"]) == r.max_tokens for o, r in zip(out, reqs))
+    with ContextSpy(engine.executor, record_contexts):
+        t0 = time.perf_counter()
+        if group is None:
+            out = engine.generate(prompts, params, use_tqdm=False)
+        else:
+            from mini_vllm_b200.dispatcher import generate_over_ranks
+            out = generate_over_ranks(engine, prompts, params, group=group)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+    n_tok = 0
+    if out is not None:
+        n_tok = sum(len(p) for p in prompts) + sum(len(o["tokens"]) for o in out)
+        assert all(len(o["tokens"]) == r.max_tokens for o, r in zip(out, reqs))
     return n_tok, wall, engine.last_job_device_ms
 
 
@@ -217,17 +236,101 @@ def decode_roofline(engine, contexts, peaks):
             "note": "algorithmic K+V bytes of recorded decode steps, 28 layer launches replayed from a CUDA graph; peak = STREAM copy"}
 
 
-def kernel_extras(dev, peaks, nl=4):
+LEGS = ("attn3", "prefill", "attn4", "sampler", "rope", "pack")
+
+
+def graph_time_ms(sweep, launches_per_sweep: int, reps: int = 5) -> float:
+    """Device time per launch of ``sweep`` (a function that enqueues ``launches_per_sweep`` kernels over
+    distinct buffers), replayed from a CUDA graph so that short kernels are not timed at the host's launch rate."""
+    sweep()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        sweep()
+    graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * launches_per_sweep)
+
+
+def rope_and_pack_legs(dev, peaks, legs) -> dict:
+    """The elementwise and integer kernels of the path on config-3 / config-5 sized steps."""
+    from mini_vllm_b200 import ops
+    from mini_vllm_b200.models.layers.rotary import build_cos_sin_cache
+    import numpy as np
+    out = {}
+    hq, hkv, d = 16, 8, 128
+    case, g = config3()
+    q_lens = [n - c for n, c in zip(case.prefill_lens, case.prefill_cached)]
+    if "rope" in legs:
+        table = build_cos_sin_cache(d, 8192, 1e6).to(dev)
+        wq = torch.ones(d, device=dev, dtype=torch.bfloat16)
+        for name, tokens in (("prefill12784", sum(q_lens)), ("decode512", 512)):
+            nbuf = max(2, min(8, int(400e6 / (tokens * (hq + 2 * hkv) * d * 2))))
+            qkvs = [torch.randn(tokens, (hq + 2 * hkv) * d, device=dev).to(torch.bfloat16) for _ in range(nbuf)]
+            pools = [torch.zeros(2, tokens // 256 + 2, 256, hkv, d, device=dev, dtype=torch.bfloat16) for _ in range(nbuf)]
+            pos = torch.arange(tokens, device=dev, dtype=torch.int64) % 4096
+            slots = torch.randperm(tokens, device=dev).to(torch.int32)          # every token its own slot, scattered
+            views = [tuple(t.view(tokens, -1, d) for t in x.split([hq * d, hkv * d, hkv * d], dim=-1)) for x in qkvs]
+            # q, k, v read where the projection left them; q written back in place, k and v to their cache slots
+            byts = tokens * (hq + 2 * hkv) * d * 2 * 2
+            for kern, call in (("rope_kv_write", lambda v3, p: ops.rope_kv_write(v3[0], v3[1], v3[2], pos, table, slots, p[0], p[1], k_in_place=False)),
+                               ("qk_norm_rope_kv_write", lambda v3, p: ops.qk_norm_rope_kv_write(v3[0], v3[1], v3[2], wq, wq, 1e-6, False, pos, table, slots, p[0], p[1], k_in_place=False))):
+                ms = graph_time_ms(lambda: [call(v3, p) for v3, p in zip(views, pools)], nbuf)
+                out[f"{kern}_{name}"] = {"GB/s": round(byts / ms / 1e6, 1), "us": round(ms * 1e3, 2), "bytes": byts,
+                                         "frac_of_measured_hbm": round(byts / ms / 1e6 / peaks["hbm_gbs"], 4)}
+            del qkvs, pools, views
+    if "pack" in legs:
+        # prefill packing of config 3's 16 prompts (12 784 new tokens, cached prefixes) and decode packing of 512 rows
+        seq_len = np.asarray(case.prefill_lens, np.int32)
+        cached = np.asarray(case.prefill_cached, np.int32)
+        nblk = np.asarray([len(b) for b in case.prefill_blocks], np.int32)
+        blk_off = np.concatenate([[0], np.cumsum(nblk)]).astype(np.int32)
+        blocks = np.concatenate([np.asarray(b, np.int32) for b in case.prefill_blocks])
+        t = int((seq_len - cached).sum())
+        toks = torch.randint(0, 151936, (t,), generator=g).numpy().astype(np.int32)
+        meta = torch.from_numpy(np.concatenate([seq_len, cached, blk_off, blocks, toks])).to(dev)
+        ms = graph_time_ms(lambda: [ops.pack_prefill(meta, 16, t, int(blk_off[-1]), int(nblk.max()), 256, True) for _ in range(8)], 8)
+        out["pack_prefill_config3"] = {"us": round(ms * 1e3, 2), "tokens": t, "out_bytes": t * 20 + 16 * int(nblk.max()) * 4}
+        b = 512
+        ctx = torch.randint(32, 5120, (b,), generator=g).numpy().astype(np.int32)
+        nb = (ctx + 255) // 256
+        off = np.concatenate([[0], np.cumsum(nb)]).astype(np.int32)
+        flat = np.arange(int(off[-1]), dtype=np.int32)
+        meta = torch.from_numpy(np.concatenate([ctx, off, flat, np.zeros(b, np.int32), np.full(b, -1, np.int32)])).to(dev)
+        ids, pos = torch.empty(b, dtype=torch.int64, device=dev), torch.empty(b, dtype=torch.int64, device=dev)
+        slot, lens = torch.empty(b, dtype=torch.int32, device=dev), torch.empty(b, dtype=torch.int32, device=dev)
+        table = torch.empty(b, 4096, dtype=torch.int32, device=dev)[:, :int(nb.max())]   # row stride of a graph runner's table
+        ms = graph_time_ms(lambda: [ops.pack_decode(meta, b, int(off[-1]), int(nb.max()), 256, ids, pos, slot, lens, table)
+                                    for _ in range(8)], 8)
+        out["pack_decode_512"] = {"us": round(ms * 1e3, 2), "rows": b, "out_bytes": b * (8 + 8 + 4 + 4 + int(nb.max()) * 4)}
+    return out
+
+
+def kernel_extras(dev, peaks, nl=4, legs=LEGS):
     """Fixed single-layer cases: the 240-sequence decode batch and the 16-sequence prefill batch.
 
     ``nl`` distinct KV pools (2.3 GB each) are rotated so that consecutive launches share nothing in L2.
     """
+    out = {}
+    if "attn3" in legs or "prefill" in legs:
+        out.update(attention_legs_qwen3(dev, peaks, nl, legs))
+    if "attn4" in legs:
+        out.update(decode_legs_gemma3(dev, peaks, nl))
+    if "sampler" in legs:
+        out.update(sampler_legs(dev, peaks))
+    out.update(rope_and_pack_legs(dev, peaks, legs))
+    return out
+
+
+def decode_leg_config3(dev, peaks, nl, case, pools, out):
     from mini_vllm_b200 import ops
     from mini_vllm_b200.workloads import table_tensor
-    case, _ = config3()
     hq, hkv, d = 16, 8, 128
-    pools = [torch.randn(2, case.pool_blocks, 256, hkv, d, device=dev, dtype=torch.bfloat16) for _ in range(nl)]
-    out = {}
     # decode part
     b = len(case.decode_ctx)
     q = torch.randn(b, hq, d, device=dev, dtype=torch.bfloat16)
@@ -236,37 +339,48 @@ def kernel_extras(dev, peaks, nl=4):
     ws = ops.decode_workspace(b, hq, d, dev)
     o = torch.empty_like(q)
     ops.decode_plan(lens, -1, hq, hkv, d, ws, block_table=bt, block_size=256)
-    iters = 24
-    for i in range(8):
-        ops.decode_attn(q, pools[i % nl][0], pools[i % nl][1], lens, bt, d ** -0.5, -1, ws, out=o)
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
-    evs[0].record()
-    for i in range(iters):
-        ops.decode_attn(q, pools[i % nl][0], pools[i % nl][1], lens, bt, d ** -0.5, -1, ws, out=o)
-        evs[i + 1].record()
-    torch.cuda.synchronize()
-    ms = statistics.median(evs[i].elapsed_time(evs[i + 1]) for i in range(iters))
+    ms = event_time_ms(lambda i: ops.decode_attn(q, pools[i % nl][0], pools[i % nl][1], lens, bt, d ** -0.5, -1, ws, out=o),
+                       24, warm=8)
     byts = decode_kv_bytes(QWEN3_0P6B, case.decode_ctx)
     gbs = byts / ms / 1e6
     out["decode_attn_config3"] = {"GB/s": round(gbs, 1), "us": round(ms * 1e3, 1), "bytes": byts,
                                   "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
                                   "frac_of_8TBs_nominal": round(gbs / 8000.0, 4)}
-    # prefill part (paged, half the sequences with a cached 512-token prefix)
-    q_lens = [n - c for n, c in zip(case.prefill_lens, case.prefill_cached)]
-    tq = sum(q_lens)
-    cu = lambda xs: torch.tensor([0] + list(torch.tensor(xs).cumsum(0)), dtype=torch.int32, device=dev)
-    qp = torch.randn(tq, hq, d, device=dev, dtype=torch.bfloat16)
-    btp = table_tensor(case.prefill_blocks).to(dev)
-    cq, ck = cu(q_lens), cu(case.prefill_lens)
-    for i in range(3):
-        ops.prefill_attn(qp, pools[0][0], pools[0][1], cq, ck, max(q_lens), d ** -0.5, -1, block_table=btp)
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(11)]
+    return out
+
+
+def event_time_ms(call, iters: int, warm: int = 3) -> float:
+    """Median device time of ``call(i)`` over ``iters`` launches, CUDA events on the launching stream."""
+    for i in range(warm):
+        call(i)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
     evs[0].record()
-    for i in range(10):
-        ops.prefill_attn(qp, pools[i % nl][0], pools[i % nl][1], cq, ck, max(q_lens), d ** -0.5, -1, block_table=btp)
+    for i in range(iters):
+        call(i)
         evs[i + 1].record()
     torch.cuda.synchronize()
-    ms = statistics.median(evs[i].elapsed_time(evs[i + 1]) for i in range(10))
+    return statistics.median(evs[i].elapsed_time(evs[i + 1]) for i in range(iters))
+
+
+def attention_legs_qwen3(dev, peaks, nl, legs):
+    from mini_vllm_b200 import ops
+    from mini_vllm_b200.workloads import table_tensor
+    case, _ = config3()
+    hq, hkv, d = 16, 8, 128
+    pools = [torch.randn(2, case.pool_blocks, 256, hkv, d, device=dev, dtype=torch.bfloat16) for _ in range(nl)]
+    out = {}
+    if "attn3" in legs:
+        decode_leg_config3(dev, peaks, nl, case, pools, out)
+    if "prefill" not in legs:
+        return out
+    cu = lambda xs: torch.tensor([0] + list(torch.tensor(xs).cumsum(0)), dtype=torch.int32, device=dev)
+    # prefill part (paged, half the sequences with a cached 512-token prefix)
+    q_lens = [n - c for n, c in zip(case.prefill_lens, case.prefill_cached)]
+    qp = torch.randn(sum(q_lens), hq, d, device=dev, dtype=torch.bfloat16)
+    btp = table_tensor(case.prefill_blocks).to(dev)
+    cq, ck = cu(q_lens), cu(case.prefill_lens)
+    ms = event_time_ms(lambda i: ops.prefill_attn(qp, pools[i % nl][0], pools[i % nl][1], cq, ck, max(q_lens), d ** -0.5,
+                                                  -1, block_table=btp), 10)
     fl = prefill_flops(QWEN3_0P6B, case.prefill_lens, case.prefill_cached)
     tf = fl / ms / 1e9
     out["prefill_attn_config3"] = {"TFLOP/s": round(tf, 1), "us": round(ms * 1e3, 1), "flops": fl,
@@ -279,21 +393,20 @@ def kernel_extras(dev, peaks, nl=4):
         kd = torch.randn(nseq * slen, hkv, d, device=dev, dtype=torch.bfloat16)
         vd = torch.randn(nseq * slen, hkv, d, device=dev, dtype=torch.bfloat16)
         cd = cu(lens_p)
-        for _ in range(3):
-            ops.prefill_attn(qd, kd, vd, cd, cd, slen, d ** -0.5, -1)
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(11)]
-        evs[0].record()
-        for i in range(10):
-            ops.prefill_attn(qd, kd, vd, cd, cd, slen, d ** -0.5, -1)
-            evs[i + 1].record()
-        torch.cuda.synchronize()
-        ms = statistics.median(evs[i].elapsed_time(evs[i + 1]) for i in range(10))
+        ms = event_time_ms(lambda i: ops.prefill_attn(qd, kd, vd, cd, cd, slen, d ** -0.5, -1), 10)
         fl = prefill_flops(QWEN3_0P6B, lens_p, [0] * nseq)
         out[name] = {"TFLOP/s": round(fl / ms / 1e9, 1), "us": round(ms * 1e3, 1), "flops": fl,
                      "frac_of_measured_bf16": round(fl / ms / 1e9 / peaks["bf16_tflops"], 4)}
         del qd, kd, vd
-    # Gemma3-1B shapes (4 q heads, 1 kv head, head_dim 256), 128 sequences, contexts U[512,4096]:
-    # a global layer and a sliding-window-512 layer (window layers count only the visible keys)
+    return out
+
+
+def decode_legs_gemma3(dev, peaks, nl):
+    """Gemma3-1B shapes (4 q heads, 1 kv head, head_dim 256), 128 sequences, contexts U[512,4096]: a global layer
+    and a sliding-window-512 layer (window layers count only the visible keys)."""
+    from mini_vllm_b200 import ops
+    from mini_vllm_b200.workloads import table_tensor
+    out = {}
     g4, _ = config4()
     hq, hkv, d = 4, 1, 256
     gpools = [torch.randn(2, g4.pool_blocks, 256, hkv, d, device=dev, dtype=torch.bfloat16) for _ in range(max(nl, 2) * 2)]
@@ -305,29 +418,19 @@ def kernel_extras(dev, peaks, nl=4):
     for name, window in (("decode_attn_config4_global", -1), ("decode_attn_config4_window512", 512)):
         ws = ops.decode_workspace(b, hq, d, dev)
         ops.decode_plan(lens, window, hq, hkv, d, ws, block_table=bt, block_size=256)
-
-        def layer_sweep():
-            for gp in gpools:
-                ops.decode_attn(q, gp[0], gp[1], lens, bt, d ** -0.5, window, ws, out=o)
-        layer_sweep()
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()                       # short kernels: time device time, not the launch rate
-        with torch.cuda.graph(graph):
-            layer_sweep()
-        graph.replay()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(5):
-            graph.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / (5 * len(gpools))
+        ms = graph_time_ms(lambda: [ops.decode_attn(q, gp[0], gp[1], lens, bt, d ** -0.5, window, ws, out=o) for gp in gpools],
+                           len(gpools))
         byts = decode_kv_bytes(GEMMA3_1B, g4.decode_ctx, window)
         gbs = byts / ms / 1e6
         out[name] = {"GB/s": round(gbs, 1), "us": round(ms * 1e3, 1), "bytes": byts,
                      "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4)}
-    del gpools
-    # sampler over Qwen3's vocabulary: the 512-row and the 64-row decode batch, greedy and top-k/top-p
+    return out
+
+
+def sampler_legs(dev, peaks):
+    """The sampler over Qwen3's vocabulary: the 512-row and the 64-row decode batch, greedy and top-k/top-p."""
+    from mini_vllm_b200 import ops
+    out = {}
     vocab = 151936
     for rows in (512, 64):
         bufs = [torch.randn(rows, vocab, device=dev).to(torch.bfloat16) for _ in range(max(2, min(16, int(600e6 / (rows * vocab * 2)))))]
@@ -336,22 +439,7 @@ def kernel_extras(dev, peaks, nl=4):
         topp = torch.full((rows,), 0.9, device=dev)
         for name, call in ((f"sample_greedy_{rows}", lambda x: ops.sample(x)),
                            (f"sample_top50_p0.9_{rows}", lambda x: ops.sample(x, temps, topk, 1, 0, top_p=topp))):
-            def sweep():
-                for x in bufs:                               # distinct buffers: nothing comes from L2
-                    call(x)
-            sweep()
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                sweep()
-            graph.replay()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(5):
-                graph.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / (5 * len(bufs))
+            ms = graph_time_ms(lambda: [call(x) for x in bufs], len(bufs))       # distinct buffers: nothing comes from L2
             byts = rows * vocab * 2
             out[name] = {"GB/s": round(byts / ms / 1e6, 1), "us": round(ms * 1e3, 1), "bytes": byts,
                          "frac_of_measured_hbm": round(byts / ms / 1e6 / peaks["hbm_gbs"], 4)}
@@ -427,57 +515,86 @@ def config4_engine_step() -> dict:
 
 
 # ---- CPU leg: the oracle restatement of the reference path on the host cores ------------------------
-def cpu_reference_sample(workload: str = "config5", budget_s: float = 20.0, seed: int = 0):
-    """Prefill + decode of a few config-2 requests through the oracle model on CPU; returns tok/s."""
-    from mini_vllm_b200.models.loader import load_model
-    from mini_vllm_b200.engine.request import Request
-    from mini_vllm_b200.scheduler.scheduler import Scheduler
-    from oracle.model import OracleExecutor, OracleModel, reference_names
-    threads = os.cpu_count() or 1
-    torch.set_num_threads(threads)
-    hf = qwen3_shape()
-    cfg = Config(hf_config=hf, kv_cache_num_blocks=160, max_num_batched_seqs=8, use_cuda_graph=False, seed=seed)
-    model = load_model(cfg, device="cpu")
-    weights = reference_names(dict(model.state_dict()), "qwen3", hf)
-    del model
-    omodel = OracleModel(weights, hf, "qwen3", 160, 256, device="cpu")
-    ex = OracleExecutor(omodel, 256)
-    n_req, n_dec = 8, 48
-    reqs = workload_requests(workload)[:n_req]
-    sch = Scheduler(cfg)
-    rs = [Request(r.prompt, SamplingParams(max_tokens=n_dec, ignore_eos=True)) for r in reqs]
-    for r in rs:
-        sch.submit(r)
-    t0 = time.perf_counter()
-    tokens = 0
-    while not sch.finished and time.perf_counter() - t0 < 4 * budget_s:
-        batch = sch.schedule()
-        out = ex.execute(batch)
-        tokens += sum(len(r.tokens) - r.num_cached_tokens for r in batch.requests) if batch.type == 0 else len(out)
-        sch.update(batch, out)
-    dt = time.perf_counter() - t0
-    sample = (f"first {n_req} requests of the workload, full prompts, {n_dec} generated tokens each, bf16 weights, "
-              "prefill+decode tokens / wall time (per-token extrapolation)")
-    return tokens / dt, threads, sample, dt
+class CpuReference:
+    """The oracle model (restatement of the reference's PyTorch path, pinned to the reference's own engine loop by
+    tests/test_reference_engine.py) on the host cores.  Built once; ``sample()`` runs one bounded sample of the
+    workload: the first requests of the share until ``prompt_tokens`` prompt tokens are reached (at least two
+    requests), full prompts, ``n_dec`` generated tokens each, through the scheduler like any job."""
+
+    def __init__(self, workload: str, prompt_tokens: int = 1200, n_dec: int = 16, seed: int = 0):
+        from mini_vllm_b200.models.loader import load_model
+        from oracle.model import OracleExecutor, OracleModel, reference_names
+        self.threads = os.cpu_count() or 1
+        torch.set_num_threads(self.threads)
+        hf = qwen3_shape()
+        self.cfg = Config(hf_config=hf, kv_cache_num_blocks=160, max_num_batched_seqs=8, use_cuda_graph=False, seed=seed)
+        model = load_model(self.cfg, device="cpu")
+        weights = reference_names(dict(model.state_dict()), "qwen3", hf)
+        del model
+        self.executor = OracleExecutor(OracleModel(weights, hf, "qwen3", 160, 256, device="cpu"), 256)
+        reqs, total = [], 0
+        for r in workload_requests(workload):
+            if len(reqs) >= 2 and total >= prompt_tokens:
+                break
+            if len(r.prompt) > 2048:                 # keep one sample to seconds: the longest prompts are skipped
+                continue
+            reqs.append(r)
+            total += len(r.prompt)
+        self.reqs, self.n_dec = reqs, n_dec
+        self.describe = (f"{len(reqs)} requests of the workload ({total} prompt tokens, prompts over 2048 skipped), "
+                         f"{n_dec} generated tokens each, bf16 weights, prefill+decode tokens / wall time "
+                         "(per-token extrapolation; prefill-heavy, which favours the CPU)")
+
+    def sample(self) -> tuple[int, float]:
+        from mini_vllm_b200.engine.request import Request
+        from mini_vllm_b200.scheduler.scheduler import Scheduler
+        sch = Scheduler(self.cfg)
+        for r in self.reqs:
+            sch.submit(Request(r.prompt, SamplingParams(max_tokens=self.n_dec, ignore_eos=True)))
+        t0 = time.perf_counter()
+        tokens = 0
+        while not sch.finished:
+            batch = sch.schedule()
+            out = self.executor.execute(batch)
+            tokens += sum(len(r.tokens) - r.num_cached_tokens for r in batch.requests) if batch.type == 0 else len(out)
+            sch.update(batch, out)
+        return tokens, time.perf_counter() - t0
+
+
+def workload_config(workload: str, world: int, requests_per_gpu: int, tokens_per_step: int, mixed: bool = False) -> dict:
+    """The ``config`` object of the bench line: both arms print the same keys and values for the same run."""
+    return {"workload": WORKLOADS[workload] + (", mixed steps" if mixed else ""), "requests_per_gpu": requests_per_gpu,
+            "parallelism": f"replicas x{world}",
+            "l2": "KV pool (28 layers, >126 MB per step) exceeds L2; kernel legs rotate distinct pools",
+            "tokens_per_step_all_gpus": tokens_per_step}
 
 
 def reference_arm(args):
+    """The reference's path on the host cores (rank 0 only): ``--warmup`` untimed and exactly ``--steps`` timed
+    bounded samples; ``ms_per_step`` x ``steps`` is the time really spent in the timed region."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    vals, secs = [], []
-    for _ in range(max(1, min(args.steps, 3))):
-        v, threads, sample, dt = cpu_reference_sample(args.workload)
-        vals.append(v)
-        secs.append(dt)
-    value = statistics.median(vals)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    cpu = CpuReference(args.workload)
+    for _ in range(args.warmup):
+        cpu.sample()
+    tokens, secs = 0, 0.0
+    for _ in range(args.steps):
+        n, dt = cpu.sample()
+        tokens += n
+        secs += dt
+    value = tokens / secs
+    mine = workload_requests(args.workload, world, 0)
+    per_step_all = sum(len(r.prompt) + r.max_tokens for k in range(world) for r in workload_requests(args.workload, world, k))
+    config = workload_config(args.workload, world, len(mine), per_step_all)
+    config["sample"] = cpu.describe
     line = {"impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(1e3 * statistics.median(secs), 1),      # one step here = the bounded sample
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * secs / args.steps, 1),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOADS[args.workload]},
-            "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": threads, "kind": "port",
-                             "sample": sample},
+            "config": config,
+            "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": cpu.threads, "kind": "port",
+                             "sample": cpu.describe, "tokens_per_sample": tokens // args.steps},
             "e2e": {"value": round(value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -490,11 +607,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-strong-scaling", action="store_true",
+                    help="skip the extra N=1 job over all 4096 config-5 requests (about a minute)")
     ap.add_argument("--workload", default="config5", choices=["config5", "config2"],
                     help="config5 (default): 512 requests per GPU, prompts log-uniform [32,4096], outputs "
                          "U[64,1024]; config2: 64 requests per GPU, prompt U[100,1024], total <= 1024")
-    ap.add_argument("--kernel-legs", action="store_true",
-                    help="profiling aid: only the fixed single-layer kernel cases (one 2.3 GB pool), then exit")
+    ap.add_argument("--kernel-legs", nargs="?", const="all", default=None, metavar="LEGS",
+                    help="only the fixed single-kernel cases (one 2.3 GB pool), then exit; optionally a comma list out "
+                         "of " + ",".join(LEGS) + " to keep a profiler capture small")
     ap.add_argument("--mixed-steps", action="store_true",
                     help="variant: prompts join steps of running decodes (Config.enable_mixed_steps)")
     ap.add_argument("--config3-step", action="store_true",
@@ -521,7 +641,11 @@ def main():
         return
     if args.kernel_legs:
         peaks, _ = measured_peaks()
-        print(json.dumps(kernel_extras(torch.device("cuda", 0), peaks, nl=1)))
+        legs = LEGS if args.kernel_legs == "all" else tuple(args.kernel_legs.split(","))
+        unknown = [x for x in legs if x not in LEGS]
+        if unknown:
+            ap.error(f"unknown kernel legs {unknown}; choose from {LEGS}")
+        print(json.dumps(kernel_extras(torch.device("cuda", 0), peaks, nl=1, legs=legs)))
         return
     if args.engine_steps:
         import dataclasses
@@ -551,6 +675,14 @@ def main():
     mine = workload_requests(args.workload, world, rank)
     engine = build_engine(local_rank, args.workload, mixed_steps=args.mixed_steps)
     dev = engine.executor.device
+    # At N > 1 the job goes through the host dispatcher: rank 0 holds every request of the job (the shares of all
+    # ranks), scatters them by token cost over a gloo group, and gets the completions back.
+    group, job = None, mine
+    if dist is not None:
+        group = dist.new_group(backend="gloo")
+        job = None
+        if rank == 0:
+            job = [r for k in range(world) for r in workload_requests(args.workload, world, k)]
 
     def sync_all():
         torch.cuda.synchronize()
@@ -559,7 +691,7 @@ def main():
             torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        run_job(engine, mine)
+        run_job(engine, job, group=group)
     sampler = ClockSampler(local_rank)
     contexts = []
     ex = engine.executor
@@ -572,7 +704,7 @@ def main():
     tok = 0
     cuda_ms = 0.0
     for i in range(args.steps):
-        n, wall, ms = run_job(engine, mine, contexts if i == args.steps - 1 else None)
+        n, wall, ms = run_job(engine, job, contexts if (rank == 0 and i == args.steps - 1) else None, group=group)
         tok += n
         cuda_ms += ms
     sync_all()
@@ -592,23 +724,33 @@ def main():
     else:
         cuda_ms_max, wall_ms_max, tok_all, launches_all = cuda_ms, wall_total * 1e3, float(tok), float(launches)
 
+    # Strong-scaling reference point, N = 1 only: the whole 4096-request job of config 5 on this one GPU, once.
+    strong = None
+    if world == 1 and args.workload == "config5" and not args.no_strong_scaling:
+        from mini_vllm_b200.workloads import config5_requests
+        n, wall, ms = run_job(engine, config5_requests(seed=0, n=4096))
+        strong = {"requests": 4096, "tokens": n, "device_ms": round(ms, 1), "tokens_per_s": round(n / ms * 1e3, 1),
+                  "e2e_tokens_per_s": round(n / wall, 1),
+                  "note": "all of config 5 on one GPU, one job; the 8-GPU run of the same 4096 requests is the N=8 line"}
+
     if rank == 0:
         roof = decode_roofline(engine, contexts, peaks)
         roof["peak_kind"] = f"of {peak_kind}"
         extras = kernel_extras(dev, peaks)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            v, threads, sample, dt = cpu_reference_sample(args.workload)
-            cpu = {"value": round(v, 2), "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample,
-                   "seconds": round(dt, 1)}
+            ref = CpuReference(args.workload)
+            ref.sample()                                                # warm-up (allocator, thread pool)
+            n1, dt1 = ref.sample()
+            n2, dt2 = ref.sample()
+            cpu = {"value": round((n1 + n2) / (dt1 + dt2), 2), "unit": "tokens/s", "cores": ref.threads, "kind": "port",
+                   "sample": ref.describe, "seconds": round(dt1 + dt2, 1)}
         line = {
             "metric": METRIC, "value": round(tok_all / (cuda_ms_max * 1e-3), 1), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(cuda_ms_max / args.steps, 2), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOADS[args.workload] + (", mixed steps" if args.mixed_steps else ""), "requests_per_gpu": len(mine), "parallelism": f"replicas x{world}",
-                       "l2": "KV pool (28 layers, >126 MB per step) exceeds L2; kernel legs rotate distinct pools",
-                       "tokens_per_step_all_gpus": int(tok_all / args.steps)},
+            "config": workload_config(args.workload, world, len(mine), int(tok_all / args.steps), args.mixed_steps),
             "e2e": {"value": round(tok_all / (wall_ms_max * 1e-3), 1), "unit": "tokens/s",
                     "h2d_bytes_per_step": int(h2d / max(engine_steps, 1)),
                     "d2h_bytes_per_step": int(d2h / max(engine_steps, 1)),
@@ -616,6 +758,12 @@ def main():
             "gpu_launches": int(launches_all),
             "clocks": clocks, "roofline": roof, "kernels": extras, "cpu_baseline": cpu,
         }
+        if strong is not None:
+            line["strong_scaling_n1_tok_s"] = strong["tokens_per_s"]
+            line["strong_scaling_n1"] = strong
+        if world > 1:
+            line["e2e"]["path"] = ("rank 0 holds all requests: host dispatcher scatter (gloo) -> Engine.generate on every "
+                                   "rank -> gather and merge on rank 0; wall clock on rank 0")
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()
