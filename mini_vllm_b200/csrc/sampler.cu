@@ -1,13 +1,20 @@
-// Fused temperature / top-k / Gumbel-max sampler (HBM-bound: algorithmic bytes = num_rows * vocab * 2):
-// greedy rows are split over a cluster of CTAs; the random path runs one CTA per row and normally
-// reads the row twice (its maximum, then the entries near it into shared memory), else four times.
+// Fused temperature / top-k / top-p / Gumbel-max sampler (HBM-bound: algorithmic bytes = num_rows * vocab * 2).
+// Every row is split over a thread-block cluster of 1-8 CTAs (chosen on the host so that a small batch still
+// fills the GPU); the slices' results meet in the cluster's first CTA through distributed shared memory.
 //
 // Greedy: argmax of float(logit) / T with the lowest index winning ties, which is what
 // torch.argmax returns on the same fp32 values.
-// Random: radix-select the k-th largest bf16 key with two 256-bin histogram passes (and, for top-p, the
-// key at which the probability mass of the kept tokens reaches top_p, with two mass histograms), then
+// Random: keep every entry >= the k-th largest, then the nucleus of probability mass top_p among those, then
 // argmax over the kept entries of  logit / T - log(-log(u)),  u from Philox4x32-10 with
 // counter (column/4, row, offset_lo, offset_hi), key (seed_lo, seed_hi), word column%4.
+//   Usual case (0 < k < vocab and the k-th largest lies within one binade of the maximum): each CTA streams its
+//   slice once for the maximum (DRAM), the cluster agrees on the row maximum, each CTA streams its slice again
+//   (L2) and moves the entries within 127 bf16 steps of the maximum - about 1 % of a row - into the first CTA's
+//   shared memory.  There the k-th key, the nucleus and the draw are found on that short list: its keys take
+//   only 128 distinct values, so ONE 128-bin count gives the k-th key exactly, and a bin's probability mass is
+//   its count times the weight of its value (no floating-point atomics).
+//   Otherwise (no top-k, a very peaked row, NaNs): the first CTA radix-selects over the whole row with two
+//   256-bin histogram passes (and two more of softmax mass for the nucleus).
 #include "common.cuh"
 #include "host_util.cuh"
 #include "mini_vllm_b200.h"
@@ -97,12 +104,55 @@ __device__ __forceinline__ void for_each_word(const uint16_t* row, int vocab, bo
   }
 }
 
+// The same over one slice of the row (part of parts, split at 16-byte vectors), with four 128-bit loads in
+// flight per thread: a CTA streaming its slice is bound by how many bytes it keeps in flight.
+template <class F>
+__device__ __forceinline__ void for_each_word_slice(const uint16_t* row, int vocab, bool vec_ok, int part, int parts, F f) {
+  if (vec_ok) {
+    const int nvec = vocab / 8;
+    const int v0 = static_cast<int>(static_cast<int64_t>(nvec) * part / parts);
+    const int v1 = static_cast<int>(static_cast<int64_t>(nvec) * (part + 1) / parts);
+    int v = v0 + threadIdx.x;
+    for (; v + 3 * kSampleThreads < v1; v += 4 * kSampleThreads) {
+      uint4 w[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) w[u] = *reinterpret_cast<const uint4*>(row + (v + u * kSampleThreads) * 8);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = (v + u * kSampleThreads) * 8;
+        f(c, w[u].x); f(c + 2, w[u].y); f(c + 4, w[u].z); f(c + 6, w[u].w);
+      }
+    }
+    for (; v < v1; v += kSampleThreads) {
+      const uint4 w = *reinterpret_cast<const uint4*>(row + v * 8);
+      f(v * 8, w.x); f(v * 8 + 2, w.y); f(v * 8 + 4, w.z); f(v * 8 + 6, w.w);
+    }
+    if (part == parts - 1) {
+      for (int c = nvec * 8 + 2 * threadIdx.x; c < vocab; c += 2 * kSampleThreads) {
+        const uint32_t lo = row[c], hi = c + 1 < vocab ? row[c + 1] : 0xff80u;   // -inf pads an odd tail
+        f(c, lo | (hi << 16));
+      }
+    }
+  } else {
+    const int c0 = static_cast<int>(static_cast<int64_t>(vocab) * part / parts) & ~1;
+    const int c1 = part == parts - 1 ? vocab : (static_cast<int>(static_cast<int64_t>(vocab) * (part + 1) / parts) & ~1);
+    for (int c = c0 + 2 * threadIdx.x; c < c1; c += 2 * kSampleThreads) {
+      const uint32_t lo = row[c], hi = c + 1 < c1 ? row[c + 1] : 0xff80u;
+      f(c, lo | (hi << 16));
+    }
+  }
+}
+
 __device__ __forceinline__ float bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
 
 // Monotone map bf16 bits -> uint16 (larger float, larger key); -0 and +0 share a key.
 __device__ __forceinline__ uint32_t sort_key(uint16_t b) {
   if (b == 0x8000u) b = 0;
   return (b & 0x8000u) ? static_cast<uint32_t>(static_cast<uint16_t>(~b)) : static_cast<uint32_t>(b | 0x8000u);
+}
+
+__device__ __forceinline__ uint16_t key_to_bits(uint32_t key) {
+  return (key & 0x8000u) ? static_cast<uint16_t>(key ^ 0x8000u) : static_cast<uint16_t>(~key);
 }
 
 __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
@@ -237,7 +287,10 @@ __global__ void __launch_bounds__(kSampleThreads) sample_greedy_kernel(const Sam
 
 constexpr int kKeptCap = 4096;       // kept (top-k) entries that the random path holds in shared memory
 
-__global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(const SampleParams p) {
+__global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(const SampleParams p) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int parts = static_cast<int>(cluster.num_blocks()), part = static_cast<int>(cluster.block_rank());
   constexpr int NW = kSampleThreads / 32;
   __shared__ uint32_t hist_w[NW][256];                       // one histogram per warp: no contention between warps
   __shared__ uint32_t hist[256];
@@ -247,15 +300,174 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
   __shared__ int32_t kept_col[kKeptCap];
   __shared__ uint16_t kept_bits[kKeptCap];
   __shared__ uint32_t n_kept_s;
-  const int r = blockIdx.x;
-  const int warp = threadIdx.x >> 5;
+  __shared__ uint32_t slice_max_s;                           // largest key of this CTA's slice (read by the cluster)
+  const int r = blockIdx.x / parts;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint16_t* row = p.logits + r * p.row_stride;
   const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
   const float temp = p.temperatures != nullptr ? p.temperatures[r] : 1.f;
   const bool scaled = p.temperatures != nullptr;
   const int k = p.top_k != nullptr ? p.top_k[r] : 0;
   const float top_p = p.top_p != nullptr ? p.top_p[r] : 1.f;
+  const uint32_t k0 = static_cast<uint32_t>(p.seed), k1 = static_cast<uint32_t>(p.seed >> 32);
+  const uint32_t o0 = static_cast<uint32_t>(p.offset), o1 = static_cast<uint32_t>(p.offset >> 32);
+  auto emit = [&](int token) {                               // thread 0
+    p.out[r] = token;
+    if (p.scatter_table != nullptr) p.scatter_table[p.scatter_index[r]] = token;
+  };
+  auto gumbel_score = [&](int c, uint16_t bits) -> float {
+    uint32_t rnd[4];
+    philox4x32_10(static_cast<uint32_t>(c >> 2), static_cast<uint32_t>(r), o0, o1, k0, k1, rnd);
+    const float u = __fmul_rn(__fadd_rn(static_cast<float>(rnd[c & 3] >> 9), 0.5f), 1.0f / 8388608.0f);
+    float x = bits_to_float(bits);
+    if (scaled) x = __fdiv_rn(x, temp);
+    return __fsub_rn(x, logf(-logf(u)));
+  };
 
+  // ---- the usual case: the k-th largest lies within one binade of the row maximum ------------------------
+  // (the whole cluster sees the same k, so either every CTA takes this branch or only the first one goes on)
+  const bool windowed = k > 0 && k < p.vocab;
+  if (!windowed && part != 0) return;
+  if (windowed) {
+    // 1. the row maximum: packed bf16 compares, 1-2 instructions per two logits; a NaN poisons the maximum,
+    //    which empties the window below and sends the row down the general way
+    __nv_bfloat162 m2 = __floats2bfloat162_rn(-INFINITY, -INFINITY);
+    for_each_word_slice(row, p.vocab, vec_ok, part, parts,
+                        [&](int, uint32_t w) { m2 = __hmax2_nan(m2, *reinterpret_cast<const __nv_bfloat162*>(&w)); });
+    const __nv_bfloat16 m1 = __hmax_nan(__low2bfloat16(m2), __high2bfloat16(m2));
+    uint32_t kmax = __reduce_max_sync(0xffffffffu, sort_key(__bfloat16_as_ushort(m1)));
+    if (lane == 0) hist[warp] = kmax;
+    if (threadIdx.x == 0) n_kept_s = 0;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const uint32_t m = __reduce_max_sync(0xffffffffu, threadIdx.x < NW ? hist[threadIdx.x] : 0u);
+      if (threadIdx.x == 0) slice_max_s = m;
+    }
+    cluster.sync();                                          // every slice maximum is published
+    if (threadIdx.x < 32) {
+      uint32_t m = 0;
+      if (threadIdx.x < parts) m = *cluster.map_shared_rank(&slice_max_s, threadIdx.x);
+      m = __reduce_max_sync(0xffffffffu, m);
+      if (threadIdx.x == 0) sel_s[0] = m;
+    }
+    __syncthreads();
+    kmax = sel_s[0];
+    // 2. everything within 127 bf16 steps of the maximum goes into this CTA's list ...
+    {
+      const uint32_t lo = kmax > 127u ? kmax - 127u : 0u;
+      const __nv_bfloat16 t1 = __ushort_as_bfloat16(key_to_bits(lo));
+      const __nv_bfloat162 t2 = __halves2bfloat162(t1, t1);
+      auto push = [&](int c, uint16_t bits) {
+        if (c >= p.vocab) return;                             // the pad of an odd last column
+        const uint32_t slot = atomicAdd(&n_kept_s, 1u);
+        if (slot < kKeptCap) { kept_col[slot] = c; kept_bits[slot] = bits; }
+      };
+      for_each_word_slice(row, p.vocab, vec_ok, part, parts, [&](int c, uint32_t w) {
+        const uint32_t ge = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w), t2);
+        if (ge == 0u) return;
+        if (ge & 0xffffu) push(c, static_cast<uint16_t>(w & 0xffffu));
+        if (ge >> 16) push(c + 1, static_cast<uint16_t>(w >> 16));
+      });
+    }
+    // 3. ... and from there into the first CTA's list, one reservation per CTA
+    if (parts > 1) {
+      __syncthreads();
+      if (part != 0) {
+        const uint32_t n_local = n_kept_s;
+        uint32_t* n_remote = cluster.map_shared_rank(&n_kept_s, 0);
+        int32_t* col_remote = cluster.map_shared_rank(kept_col, 0);
+        uint16_t* bits_remote = cluster.map_shared_rank(kept_bits, 0);
+        if (threadIdx.x == 0) sel_s[1] = atomicAdd(n_remote, n_local);
+        __syncthreads();
+        const uint32_t base = sel_s[1];
+        for (uint32_t i = threadIdx.x; i < n_local && i < kKeptCap; i += kSampleThreads) {
+          const uint32_t slot = base + i;
+          if (slot < kKeptCap) { col_remote[slot] = kept_col[i]; bits_remote[slot] = kept_bits[i]; }
+        }
+      }
+      cluster.sync();                                        // the first CTA's list is complete; the others are done
+      if (part != 0) return;
+    } else {
+      __syncthreads();
+    }
+    const uint32_t n = n_kept_s;
+    if (n >= static_cast<uint32_t>(k) && n <= kKeptCap) {
+      // 4. the list's keys are kmax - 0 .. kmax - 127: one count per distance from the maximum
+      for (int i = threadIdx.x; i < 128; i += kSampleThreads) hist[i] = 0;
+      __syncthreads();
+      for (uint32_t i = threadIdx.x; i < n; i += kSampleThreads) atomicAdd(&hist[kmax - sort_key(kept_bits[i])], 1u);
+      __syncthreads();
+      if (warp == 0) {
+        // lane owns distances 4 * lane .. 4 * lane + 3 (ascending distance = descending value)
+        uint32_t cnt[4], mine = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { cnt[j] = hist[4 * lane + j]; mine += cnt[j]; }
+        uint32_t incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += up;
+        }
+        uint32_t cum = incl - mine, kth = 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          cum += cnt[j];
+          if (kth == 128 && cum >= static_cast<uint32_t>(k)) kth = 4 * lane + j;
+        }
+        kth = __reduce_min_sync(0xffffffffu, kth);           // distance of the k-th largest (n >= k: it exists)
+        if (top_p < 1.f) {
+          // nucleus among the kept: a bin's mass is its count times exp(value / T - max / T)
+          float xmax = bits_to_float(key_to_bits(kmax));
+          if (scaled) xmax = __fdiv_rn(xmax, temp);
+          float m[4], msum = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t dist = 4 * lane + j;
+            m[j] = 0.f;
+            if (cnt[j] != 0u && dist <= kth) {
+              float x = bits_to_float(key_to_bits(kmax - dist));
+              if (scaled) x = __fdiv_rn(x, temp);
+              m[j] = static_cast<float>(cnt[j]) * expf(x - xmax);
+            }
+            msum += m[j];
+          }
+          float mincl = msum;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, mincl, o);
+            if (lane >= o) mincl += up;
+          }
+          const float need = top_p * __shfl_sync(0xffffffffu, mincl, 31);
+          float mc = mincl - msum;
+          uint32_t cut = 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            mc += m[j];
+            if (cut == 128 && m[j] > 0.f && mc >= need) cut = 4 * lane + j;
+          }
+          cut = __reduce_min_sync(0xffffffffu, cut);
+          kth = cut < kth ? cut : kth;
+        }
+        if (lane == 0) sel_s[0] = kth;
+      }
+      __syncthreads();
+      const uint32_t max_dist = sel_s[0];
+      Best b{-INFINITY, 0x7fffffff};
+      for (uint32_t i = threadIdx.x; i < n; i += kSampleThreads) {
+        const uint16_t bits = kept_bits[i];
+        if (kmax - sort_key(bits) > max_dist) continue;
+        const int c = kept_col[i];
+        const float score = gumbel_score(c, bits);
+        if (better(score, c, b.val, b.idx)) { b.val = score; b.idx = c; }
+      }
+      b = block_argmax(b);
+      if (threadIdx.x == 0) emit(b.idx);
+      return;
+    }
+    __syncthreads();                                         // the list is of no use: the general way, from scratch
+  }
+
+  // ---- the general way: radix selection over the whole row (first CTA of the cluster only) -----------------
   // counts of one byte of the key (entries for which keep(key) holds), summed into hist; over the row or,
   // once the candidates sit in shared memory, over those
   auto count_pass = [&](bool from_kept, auto bin_of, auto keep) {
@@ -322,53 +534,11 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
 
   uint32_t thresh = 0;                                       // keep keys >= thresh
   bool compact = false;                                      // the candidates sit in shared memory
-  if (k > 0 && k < p.vocab) {
-    // First attempt, two reads of the row and hardly an atomic: the largest key, then everything within
-    // one binade below it (128 bf16 steps) into shared memory.  If that holds at least k entries and
-    // fits, the k-th key is found there.
-    // (both reads compare packed bf16 pairs: 1-2 instructions per two logits; a NaN in the row makes the
-    // window empty and the general way takes over)
-    __nv_bfloat162 m2 = __floats2bfloat162_rn(-INFINITY, -INFINITY);
-    for_each_word(row, p.vocab, vec_ok, [&](int, uint32_t w) { m2 = __hmax2_nan(m2, *reinterpret_cast<const __nv_bfloat162*>(&w)); });
-    const __nv_bfloat16 m1 = __hmax_nan(__low2bfloat16(m2), __high2bfloat16(m2));
-    uint32_t kmax = sort_key(__bfloat16_as_ushort(m1));
-    kmax = __reduce_max_sync(0xffffffffu, kmax);
-    if ((threadIdx.x & 31) == 0) hist[warp] = kmax;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-      const uint32_t m = __reduce_max_sync(0xffffffffu, threadIdx.x < NW ? hist[threadIdx.x] : 0u);
-      if (threadIdx.x == 0) { sel_s[0] = m; n_kept_s = 0; }
-    }
-    __syncthreads();
-    kmax = sel_s[0];
-    {
-      const uint32_t lo = kmax > 127u ? kmax - 127u : 0u;
-      const uint16_t lo_bits = (lo & 0x8000u) ? static_cast<uint16_t>(lo ^ 0x8000u) : static_cast<uint16_t>(~lo);
-      const __nv_bfloat16 t1 = __ushort_as_bfloat16(lo_bits);
-      const __nv_bfloat162 t2 = __halves2bfloat162(t1, t1);
-      auto push = [&](int c, uint16_t bits) {
-        if (c >= p.vocab) return;                             // the pad of an odd last column
-        const uint32_t slot = atomicAdd(&n_kept_s, 1u);
-        if (slot < kKeptCap) { kept_col[slot] = c; kept_bits[slot] = bits; }
-      };
-      for_each_word(row, p.vocab, vec_ok, [&](int c, uint32_t w) {
-        const uint32_t ge = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w), t2);
-        if (ge == 0u) return;
-        if (ge & 0xffffu) push(c, static_cast<uint16_t>(w & 0xffffu));
-        if (ge >> 16) push(c + 1, static_cast<uint16_t>(w >> 16));
-      });
-      __syncthreads();
-    }
-    if (n_kept_s >= static_cast<uint32_t>(k) && n_kept_s <= kKeptCap) {
-      thresh = kth_key(true);
-      compact = true;
-    } else {
-      // the general way: radix select over the whole row, then the kept entries (k of them, plus ties
-      // at the threshold) into shared memory if they fit
-      thresh = kth_key(false);
-      gather(thresh);
-      compact = n_kept_s <= kKeptCap;
-    }
+  if (windowed) {
+    // the kept entries (k of them, plus ties at the threshold) into shared memory if they fit
+    thresh = kth_key(false);
+    gather(thresh);
+    compact = n_kept_s <= kKeptCap;
   }
   const int n_kept = compact ? static_cast<int>(n_kept_s) : 0;
   // f(column, bits) for every entry with key >= thresh
@@ -442,12 +612,10 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
     __syncthreads();
   }
 
-  const uint32_t k0 = static_cast<uint32_t>(p.seed), k1 = static_cast<uint32_t>(p.seed >> 32);
-  const uint32_t o0 = static_cast<uint32_t>(p.offset), o1 = static_cast<uint32_t>(p.offset >> 32);
   Best b{-INFINITY, 0x7fffffff};
-  uint32_t rnd[4];
-  int rnd_group = -1;
   // (the compacted list was made with the top-k threshold; the nucleus may have raised it since)
+  uint32_t rnd[4];
+  int rnd_group = -1;                                        // a whole-row pass meets the 4 columns of a Philox block in turn
   for_each_kept([&](int c, uint16_t bits) {
     if (sort_key(bits) < thresh) return;
     if ((c >> 2) != rnd_group) {
@@ -461,10 +629,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_gumbel_kernel(cons
     if (better(score, c, b.val, b.idx)) { b.val = score; b.idx = c; }
   });
   b = block_argmax(b);
-  if (threadIdx.x == 0) {
-    p.out[r] = b.idx;
-    if (p.scatter_table != nullptr) p.scatter_table[p.scatter_index[r]] = b.idx;
-  }
+  if (threadIdx.x == 0) emit(b.idx);
 }
 
 }  // namespace mvb
@@ -481,21 +646,20 @@ extern "C" int mvb_sample(const void* logits, int64_t row_stride, int num_rows, 
   SampleParams p{static_cast<const uint16_t*>(logits), row_stride, vocab, temperatures, top_k, top_p, seed, offset,
                  out, scatter_table, scatter_index};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (top_k == nullptr && top_p == nullptr) {
-    // enough CTAs for two per SM: a cluster of up to 8 per row when the batch is small
-    int parts = 1;
-    while (parts < 8 && static_cast<int64_t>(num_rows) * parts < 2 * sm_count()) parts *= 2;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(num_rows) * parts);
-    cfg.blockDim = dim3(kSampleThreads);
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = parts; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, sample_greedy_kernel, p) == cudaSuccess ? kOk : kLaunchFailed;
-  }
-  sample_topk_gumbel_kernel<<<num_rows, kSampleThreads, 0, st>>>(p);
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+  // enough CTAs for two per SM: a cluster of up to 8 per row when the batch is small
+  int parts = 1;
+  while (parts < 8 && static_cast<int64_t>(num_rows) * parts < 2 * sm_count()) parts *= 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(num_rows) * parts);
+  cfg.blockDim = dim3(kSampleThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = parts; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const bool greedy = top_k == nullptr && top_p == nullptr;
+  const cudaError_t err = greedy ? cudaLaunchKernelEx(&cfg, sample_greedy_kernel, p)
+                                 : cudaLaunchKernelEx(&cfg, sample_topk_gumbel_kernel, p);
+  return err == cudaSuccess ? kOk : kLaunchFailed;
 }

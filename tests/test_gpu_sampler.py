@@ -127,3 +127,61 @@ def test_top_p_without_top_k_tensor(cuda):
     top_p = torch.tensor([1e-6, 1e-6, 1e-6, 1e-6])              # nucleus = the single most likely token
     out = ops.sample(logits.to(cuda), None, None, 5, 0, top_p=top_p.to(cuda)).cpu()
     assert torch.equal(out, osamp.greedy(logits))
+
+
+def check_against_oracle(cuda, logits, temps, top_k, top_p, seed, offset, min_exact=0.9):
+    B = logits.shape[0]
+    out = ops.sample(logits.to(cuda), None if temps is None else temps.to(cuda), None if top_k is None else top_k.to(cuda),
+                     seed, offset, top_p=None if top_p is None else top_p.to(cuda)).cpu()
+    scores = osamp.gumbel_scores(logits, temps, top_k, seed, offset, top_p=top_p)
+    picked = scores[torch.arange(B), out]
+    best = scores.max(dim=-1).values
+    ok = torch.isfinite(picked) & ((best - picked).abs() <= 1e-4)
+    assert ok.float().mean().item() >= min_exact, (out, scores.argmax(-1))
+    return out, scores
+
+
+@pytest.mark.parametrize("B", [1, 3, 40, 200, 400])
+def test_topk_rows_split_over_clusters_of_every_size(cuda, B):
+    """A row is split over 8, 4, 2 or 1 CTAs depending on the batch; the candidates of all slices meet in the first
+    CTA.  Winners in the first, a middle and the last slice, and rows whose k-th value ties with many others."""
+    V = 151936
+    g = generator(300 + B)
+    logits = randn_bf16(g, B, V) * 2
+    top_k = torch.full((B,), 50, dtype=torch.int32)
+    top = logits.max().item()
+    logits[0, 3] = top + 1.0; logits[0, V // 2 + 11] = top + 1.0; logits[0, V - 1] = top + 1.0   # one value in three slices
+    top_k[0] = 2                                               # the k-th value is tied: all three stay in
+    if B > 2:
+        logits[1, :] = -3.0
+        logits[1, 100:180] = 1.5                               # 80 equal candidates for k = 50: every one of them is kept
+        logits[2, V - 7:] = top + 2.0
+        top_k[2] = 7
+    temps = torch.full((B,), 0.9)
+    out, scores = check_against_oracle(cuda, logits, temps, top_k, None, 4242, 3, min_exact=0.95)
+    assert out[0] in (3, V // 2 + 11, V - 1)
+    if B > 2:
+        assert 100 <= out[1] < 180 and out[2] >= V - 7
+
+
+def test_topk_rows_that_leave_the_window(cuda):
+    """Rows the short-list way cannot handle fall back to radix selection over the whole row: a maximum so far
+    above the rest that fewer than k entries lie within one binade of it, k larger than the list can hold, a NaN
+    in the row, a row of one repeated value, top-k off (k = 0) with and without a nucleus."""
+    V = 151936
+    g = generator(77)
+    logits = randn_bf16(g, 8, V)
+    logits[0, 1234] = 60.0                                     # nothing else within one binade
+    logits[2, 999] = float("nan")
+    logits[3, :] = 0.25
+    top_k = torch.tensor([40, 6000, 30, 10, 0, 0, 50, 50], dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 1.0, 0.6, 1.0, 0.3, 1e-6])
+    temps = torch.tensor([1.0, 0.8, 1.0, 1.0, 0.7, 1.2, 1.0, 1.0])
+    out = ops.sample(logits.to(cuda), temps.to(cuda), top_k.to(cuda), 5, 9, top_p=top_p.to(cuda)).cpu()
+    keep = [0, 1, 3, 4, 5, 6, 7]                               # (the oracle's topk has no defined order for a NaN row)
+    full = osamp.gumbel_scores(torch.nan_to_num(logits, nan=0.0), temps, top_k, 5, 9, top_p=top_p)
+    for r in keep:
+        assert torch.isfinite(full[r, out[r]]), f"row {r}: token {out[r]} is outside the kept set"
+        assert (full[r].max() - full[r, out[r]]).abs().item() <= 1e-4, f"row {r}"
+    assert out[7] == logits[7].float().argmax()                # a nucleus of one token
+    assert 0 <= out[2] < V
