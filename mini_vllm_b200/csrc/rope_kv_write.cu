@@ -1,13 +1,14 @@
-// Fused rotary embedding + paged KV-cache write (HBM-bound elementwise pass).
+// Fused rotary embedding + paged KV-cache write (HBM-bound elementwise pass), optionally with the per-head
+// RMSNorm of q and k in front.
 //
-// One thread owns one 16-byte chunk pair: 8 bf16 of the first half of a head and the matching
-// 8 of the second half (rotate-half pairs element i with i + D/2), or one 16-byte chunk of V.
-// q is rotated in place, k is rotated and scattered to the cache slot (and optionally written
-// back), v is copied to the cache slot.  All global accesses are 128-bit.
+// q is rotated in place, k is rotated and scattered to the cache slot (and optionally written back), v is
+// copied to the cache slot.  All global accesses are 128-bit; rotate-half pairs element i with i + D/2, so a
+// task is one 16-byte chunk of the first half of a head together with its partner in the second half.
 //
 // Algorithmic bytes per token: (Hq + 2*Hkv) * D * 2 read + (Hq + 2*Hkv) * D * 2 written
 // (+ the token's cos/sin row, 4*D bytes, shared by all heads through L1/L2).
 #include "common.cuh"
+#include "host_util.cuh"
 #include "mini_vllm_b200.h"
 
 namespace mvb {
@@ -48,75 +49,19 @@ __device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float* cs, c
   }
 }
 
-__global__ void __launch_bounds__(256) rope_kv_write_kernel(const RopeParams p) {
-  const int pairs_per_head = p.d / 16;                       // chunk pairs per head
-  const int rope_tasks = (p.hq + p.hkv) * pairs_per_head;    // per token
-  const int v_tasks = p.hkv * p.d / 8;
-  const int tasks = rope_tasks + v_tasks;
-  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (gid >= static_cast<int64_t>(p.num_tokens) * tasks) return;
-  const int t = static_cast<int>(gid / tasks);
-  const int task = static_cast<int>(gid - static_cast<int64_t>(t) * tasks);
-
-  int64_t slot = -1;
-  if (p.slot_mapping != nullptr) {
-    slot = p.slot_mapping[t];
-    if (slot >= p.num_slots || slot < -1) {
-      report(p.dev_status, kDevBadSlot, t);
-      slot = -1;
-    }
-  }
-
-  if (task >= rope_tasks) {                                  // ---- V: plain copy to the cache slot
-    if (slot < 0) return;
-    const int c = task - rope_tasks;                         // 16-byte chunk within the token's V row
-    const uint4 val = *reinterpret_cast<const uint4*>(p.v + t * p.v_stride + c * 8);
-    *reinterpret_cast<uint4*>(p.v_cache + slot * (static_cast<int64_t>(p.hkv) * p.d) + c * 8) = val;
-    return;
-  }
-
-  const int head = task / pairs_per_head;                    // 0..hq-1 are q heads, then k heads
-  const int c = task - head * pairs_per_head;                // chunk pair within the head
-  const bool is_q = head < p.hq;
-  __nv_bfloat16* row = is_q ? p.q + t * p.q_stride + head * p.d : p.k + t * p.k_stride + (head - p.hq) * p.d;
-  if (!is_q && slot < 0 && !p.k_in_place) return;            // nothing to produce for this k chunk
-  if (is_q && p.cos_sin == nullptr) return;                  // plain store_kvcache leaves q alone
-
-  uint4 lo = *reinterpret_cast<const uint4*>(row + c * 8);
-  uint4 hi = *reinterpret_cast<const uint4*>(row + p.d / 2 + c * 8);
-  if (p.cos_sin != nullptr) {
-    const int64_t pos = p.positions[t];
-    if (pos < 0 || pos >= p.max_pos) {
-      report(p.dev_status, kDevBadPosition, t);
-    } else {
-      const float* tab = p.cos_sin + pos * p.d;
-      float cs[8], sn[8];
-      *reinterpret_cast<float4*>(cs) = *reinterpret_cast<const float4*>(tab + c * 8);
-      *reinterpret_cast<float4*>(cs + 4) = *reinterpret_cast<const float4*>(tab + c * 8 + 4);
-      *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(tab + p.d / 2 + c * 8);
-      *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(tab + p.d / 2 + c * 8 + 4);
-      rotate8(lo, hi, cs, sn);
-    }
-  }
-  if (is_q || p.k_in_place) {
-    if (p.cos_sin != nullptr) {
-      *reinterpret_cast<uint4*>(row + c * 8) = lo;
-      *reinterpret_cast<uint4*>(row + p.d / 2 + c * 8) = hi;
-    }
-  }
-  if (!is_q && slot >= 0) {
-    __nv_bfloat16* dst = p.k_cache + slot * (static_cast<int64_t>(p.hkv) * p.d) + (head - p.hq) * p.d;
-    *reinterpret_cast<uint4*>(dst + c * 8) = lo;
-    *reinterpret_cast<uint4*>(dst + p.d / 2 + c * 8) = hi;
-  }
-}
-
-// ---- variant with the per-head RMSNorm of q and k fused in front of the rotation ------------------
-// q/k/v are read where the projection GEMM left them (row strides of the packed output), each head
-// row is normalised in fp32 (y = x * rsqrt(mean(x^2) + eps) * w, or * (1 + w) for Gemma), rounded to
-// bf16 as the separate norm kernel would, rotated, and written: q in place, k to the cache (and in
-// place when asked), v to the cache.  The D/16 threads of a head row are consecutive lanes, so the
-// sum of squares is a shuffle reduction inside an aligned lane group.
+// ---- the kernel ------------------------------------------------------------------------------------------
+// A token's work is (Hq + Hkv) * D/16 rotation tasks (a 16-byte chunk of the first half of a head with its
+// partner in the second half) followed by Hkv * D/8 copy tasks (a 16-byte chunk of V).  A warp takes ITEMS
+// consecutive groups of 32 tasks of ONE token: every lane first issues all its loads (up to 2 * ITEMS
+// independent 128-bit loads, plus the token's slot, position and cos/sin entries), then rotates and stores.
+// With D/16 dividing 32 a lane meets the same chunk index in every group, so its cos/sin values are loaded
+// once per token.  ITEMS is chosen on the host: large for long prefills (bytes in flight per thread bound the
+// bandwidth), 1 for decode batches (enough warps to cover the GPU matter more).
+//
+// NORM adds the per-head RMSNorm of q and k in front of the rotation: each head row is normalised in fp32
+// (y = x * rsqrt(mean(x^2) + eps) * w, or * (1 + w) for Gemma), rounded to bf16 as the separate norm kernel
+// would, then rotated.  The D/16 lanes of a head row are consecutive lanes of an aligned group, so the sum of
+// squares is a shuffle reduction inside the group.
 struct NormRopeParams {
   RopeParams r;
   const __nv_bfloat16* q_weight;
@@ -125,91 +70,137 @@ struct NormRopeParams {
   int unit_offset;
 };
 
-__global__ void __launch_bounds__(256) qk_norm_rope_kv_write_kernel(const NormRopeParams np) {
+template <int ITEMS, bool NORM>
+__global__ void __launch_bounds__(256) rope_kv_kernel(const NormRopeParams np) {
   const RopeParams& p = np.r;
-  const int pairs_per_head = p.d / 16;
-  const int rope_tasks = (p.hq + p.hkv) * pairs_per_head;
-  const int v_tasks = p.hkv * p.d / 8;
-  const int tasks = rope_tasks + v_tasks;
-  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const bool in_range = gid < static_cast<int64_t>(p.num_tokens) * tasks;
-  const int t = in_range ? static_cast<int>(gid / tasks) : 0;
-  const int task = in_range ? static_cast<int>(gid - static_cast<int64_t>(t) * tasks) : tasks;   // tasks = idle
-  const bool is_rope = task < rope_tasks;
+  const int pph = p.d / 16;                                  // chunk pairs per head
+  const int rope_tasks = (p.hq + p.hkv) * pph;               // per token
+  const int tasks = rope_tasks + p.hkv * p.d / 8;
+  const int groups = (tasks + 31) >> 5;
+  const int warps_per_token = (groups + ITEMS - 1) / ITEMS;
+  const int64_t gwarp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t t64 = gwarp / warps_per_token;
+  if (t64 >= p.num_tokens) return;                           // warp-uniform
+  const int t = static_cast<int>(t64);
+  const int task0 = static_cast<int>(gwarp - t64 * warps_per_token) * (ITEMS * 32) + lane;
+  const bool rotate = p.cos_sin != nullptr;
 
-  int64_t slot = -1;
-  if (in_range && p.slot_mapping != nullptr) {
-    slot = p.slot_mapping[t];
-    if (slot >= p.num_slots || slot < -1) {
-      report(p.dev_status, kDevBadSlot, t);
-      slot = -1;
-    }
-  }
-  if (in_range && !is_rope && slot >= 0) {                   // V: plain copy to the cache slot
-    const int c = task - rope_tasks;
-    const uint4 val = *reinterpret_cast<const uint4*>(p.v + t * p.v_stride + c * 8);
-    *reinterpret_cast<uint4*>(p.v_cache + slot * (static_cast<int64_t>(p.hkv) * p.d) + c * 8) = val;
-  }
-
-  const int head = is_rope ? task / pairs_per_head : 0;
-  const int c = is_rope ? task - head * pairs_per_head : 0;
-  const bool is_q = head < p.hq;
-  __nv_bfloat16* row = is_q ? p.q + t * p.q_stride + head * p.d : p.k + t * p.k_stride + (head - p.hq) * p.d;
-  uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
-  float ss = 0.f;
-  if (is_rope) {
-    lo = *reinterpret_cast<const uint4*>(row + c * 8);
-    hi = *reinterpret_cast<const uint4*>(row + p.d / 2 + c * 8);
-    const uint32_t* a = reinterpret_cast<const uint32_t*>(&lo);
-    const uint32_t* b = reinterpret_cast<const uint32_t*>(&hi);
+  // ---- every load of this lane goes out before anything is used ------------------------------------------
+  int64_t slot = p.slot_mapping != nullptr ? static_cast<int64_t>(p.slot_mapping[t]) : -1;
+  const int64_t pos = rotate ? p.positions[t] : 0;
+  uint4 lo[ITEMS], hi[ITEMS];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float x0 = bf16_lo(a[i]), x1 = bf16_hi(a[i]), y0 = bf16_lo(b[i]), y1 = bf16_hi(b[i]);
-      ss += x0 * x0 + x1 * x1 + y0 * y0 + y1 * y1;
+  for (int j = 0; j < ITEMS; ++j) {
+    const int task = task0 + 32 * j;
+    lo[j] = make_uint4(0, 0, 0, 0); hi[j] = make_uint4(0, 0, 0, 0);
+    if (task < rope_tasks) {
+      const int head = task / pph, c = task - head * pph;
+      const __nv_bfloat16* row = head < p.hq ? p.q + t * p.q_stride + head * p.d : p.k + t * p.k_stride + (head - p.hq) * p.d;
+      lo[j] = *reinterpret_cast<const uint4*>(row + c * 8);
+      hi[j] = *reinterpret_cast<const uint4*>(row + p.d / 2 + c * 8);
+    } else if (task < tasks) {
+      lo[j] = *reinterpret_cast<const uint4*>(p.v + t * p.v_stride + (task - rope_tasks) * 8);
     }
   }
-  // every thread of the warp takes part; a head's lanes form an aligned group of pairs_per_head
-  for (int off = 1; off < pairs_per_head; off <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-  if (!is_rope) return;
-  if (!is_q && slot < 0 && !p.k_in_place) return;
-
-  const float rstd = rsqrtf(ss / static_cast<float>(p.d) + np.eps);
-  const __nv_bfloat16* w = is_q ? np.q_weight : np.k_weight;
-  {
-    const uint4 wl = *reinterpret_cast<const uint4*>(w + c * 8);
-    const uint4 wh = *reinterpret_cast<const uint4*>(w + p.d / 2 + c * 8);
-    uint32_t* a = reinterpret_cast<uint32_t*>(&lo);
-    uint32_t* b = reinterpret_cast<uint32_t*>(&hi);
-    const uint32_t* wa = reinterpret_cast<const uint32_t*>(&wl);
-    const uint32_t* wb = reinterpret_cast<const uint32_t*>(&wh);
-    const float one = np.unit_offset ? 1.f : 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      a[i] = pack_bf16(bf16_lo(a[i]) * rstd * (one + bf16_lo(wa[i])), bf16_hi(a[i]) * rstd * (one + bf16_hi(wa[i])));
-      b[i] = pack_bf16(bf16_lo(b[i]) * rstd * (one + bf16_lo(wb[i])), bf16_hi(b[i]) * rstd * (one + bf16_hi(wb[i])));
-    }
+  if (slot >= p.num_slots || slot < -1) {
+    report(p.dev_status, kDevBadSlot, t);
+    slot = -1;
   }
-  const int64_t pos = p.positions[t];
-  if (pos < 0 || pos >= p.max_pos) {
-    report(p.dev_status, kDevBadPosition, t);
-  } else {
+  const bool pos_ok = pos >= 0 && pos < p.max_pos;
+  if (rotate && !pos_ok && task0 < rope_tasks) report(p.dev_status, kDevBadPosition, t);
+  const bool same_chunk = (32 % pph) == 0;                   // the lane's chunk index does not depend on the group
+  float cs[8], sn[8];
+  auto load_table = [&](int c) {
     const float* tab = p.cos_sin + pos * p.d;
-    float cs[8], sn[8];
     *reinterpret_cast<float4*>(cs) = *reinterpret_cast<const float4*>(tab + c * 8);
     *reinterpret_cast<float4*>(cs + 4) = *reinterpret_cast<const float4*>(tab + c * 8 + 4);
     *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(tab + p.d / 2 + c * 8);
     *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(tab + p.d / 2 + c * 8 + 4);
-    rotate8(lo, hi, cs, sn);
+  };
+  if (rotate && pos_ok && same_chunk && task0 < rope_tasks) load_table(task0 % pph);
+
+  // ---- rotate and store -------------------------------------------------------------------------------------
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    const int task = task0 + 32 * j;
+    const bool is_rope = task < rope_tasks;
+    const int head = is_rope ? task / pph : 0;
+    const int c = is_rope ? task - head * pph : 0;
+    const bool is_q = head < p.hq;
+    if (NORM) {
+      float ss = 0.f;
+      if (is_rope) {
+        const uint32_t* a = reinterpret_cast<const uint32_t*>(&lo[j]);
+        const uint32_t* b = reinterpret_cast<const uint32_t*>(&hi[j]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float x0 = bf16_lo(a[i]), x1 = bf16_hi(a[i]), y0 = bf16_lo(b[i]), y1 = bf16_hi(b[i]);
+          ss += x0 * x0 + x1 * x1 + y0 * y0 + y1 * y1;
+        }
+      }
+      // every lane of the warp takes part; a head's lanes form an aligned group of pph
+      for (int off = 1; off < pph; off <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+      if (is_rope && (is_q || slot >= 0 || p.k_in_place)) {
+        const float rstd = rsqrtf(ss / static_cast<float>(p.d) + np.eps);
+        const __nv_bfloat16* w = is_q ? np.q_weight : np.k_weight;
+        const uint4 wl = *reinterpret_cast<const uint4*>(w + c * 8);
+        const uint4 wh = *reinterpret_cast<const uint4*>(w + p.d / 2 + c * 8);
+        uint32_t* a = reinterpret_cast<uint32_t*>(&lo[j]);
+        uint32_t* b = reinterpret_cast<uint32_t*>(&hi[j]);
+        const uint32_t* wa = reinterpret_cast<const uint32_t*>(&wl);
+        const uint32_t* wb = reinterpret_cast<const uint32_t*>(&wh);
+        const float one = np.unit_offset ? 1.f : 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          a[i] = pack_bf16(bf16_lo(a[i]) * rstd * (one + bf16_lo(wa[i])), bf16_hi(a[i]) * rstd * (one + bf16_hi(wa[i])));
+          b[i] = pack_bf16(bf16_lo(b[i]) * rstd * (one + bf16_lo(wb[i])), bf16_hi(b[i]) * rstd * (one + bf16_hi(wb[i])));
+        }
+      }
+    }
+    if (task >= tasks) continue;
+    if (!is_rope) {                                          // ---- V: plain copy to the cache slot
+      if (slot >= 0)
+        *reinterpret_cast<uint4*>(p.v_cache + slot * (static_cast<int64_t>(p.hkv) * p.d) + (task - rope_tasks) * 8) = lo[j];
+      continue;
+    }
+    if (!is_q && slot < 0 && !p.k_in_place) continue;        // nothing to produce for this k chunk
+    if (is_q && !rotate && !NORM) continue;                  // plain store_kvcache leaves q alone
+    if (rotate && pos_ok) {
+      if (!same_chunk) load_table(c);
+      rotate8(lo[j], hi[j], cs, sn);
+    }
+    __nv_bfloat16* row = is_q ? p.q + t * p.q_stride + head * p.d : p.k + t * p.k_stride + (head - p.hq) * p.d;
+    if ((is_q || p.k_in_place) && (rotate || NORM)) {
+      *reinterpret_cast<uint4*>(row + c * 8) = lo[j];
+      *reinterpret_cast<uint4*>(row + p.d / 2 + c * 8) = hi[j];
+    }
+    if (!is_q && slot >= 0) {
+      __nv_bfloat16* dst = p.k_cache + slot * (static_cast<int64_t>(p.hkv) * p.d) + (head - p.hq) * p.d;
+      *reinterpret_cast<uint4*>(dst + c * 8) = lo[j];
+      *reinterpret_cast<uint4*>(dst + p.d / 2 + c * 8) = hi[j];
+    }
   }
-  if (is_q || p.k_in_place) {
-    *reinterpret_cast<uint4*>(row + c * 8) = lo;
-    *reinterpret_cast<uint4*>(row + p.d / 2 + c * 8) = hi;
-  }
-  if (!is_q && slot >= 0) {
-    __nv_bfloat16* dst = p.k_cache + slot * (static_cast<int64_t>(p.hkv) * p.d) + (head - p.hq) * p.d;
-    *reinterpret_cast<uint4*>(dst + c * 8) = lo;
-    *reinterpret_cast<uint4*>(dst + p.d / 2 + c * 8) = hi;
-  }
+}
+
+template <bool NORM>
+static int launch_rope(const NormRopeParams& np, cudaStream_t stream) {
+  const RopeParams& p = np.r;
+  const int64_t tasks = static_cast<int64_t>(p.hq + p.hkv) * (p.d / 16) + static_cast<int64_t>(p.hkv) * p.d / 8;
+  const int64_t groups = (tasks + 31) / 32;
+  // enough warps to give every SM a few blocks come first; beyond that, more loads in flight per thread
+  const int64_t want_warps = static_cast<int64_t>(sm_count()) * 32;
+  int items = 1;
+  if (groups >= 5 && p.num_tokens * ((groups + 4) / 5) >= want_warps) items = 5;
+  else if (groups >= 2 && p.num_tokens * ((groups + 1) / 2) >= want_warps) items = 2;
+  const int64_t warps = p.num_tokens * ((groups + items - 1) / items);
+  const int64_t blocks = (warps * 32 + 255) / 256;
+  if (blocks > 0x7fffffffLL) return kInvalidArgument;
+  const unsigned grid = static_cast<unsigned>(blocks);
+  if (items == 5) rope_kv_kernel<5, NORM><<<grid, 256, 0, stream>>>(np);
+  else if (items == 2) rope_kv_kernel<2, NORM><<<grid, 256, 0, stream>>>(np);
+  else rope_kv_kernel<1, NORM><<<grid, 256, 0, stream>>>(np);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -245,13 +236,10 @@ extern "C" int mvb_rope_kv_write(void* q, int64_t q_row_stride, void* k, int64_t
   p.num_tokens = num_tokens; p.hq = num_q_heads; p.hkv = num_kv_heads; p.d = head_dim;
   p.k_in_place = k_in_place;
   p.dev_status = dev_status;
-  const int64_t tasks = static_cast<int64_t>(num_q_heads + num_kv_heads) * (head_dim / 16) +
-                        static_cast<int64_t>(num_kv_heads) * head_dim / 8;
-  const int64_t total = tasks * num_tokens;
-  const int64_t blocks = (total + 255) / 256;
-  if (blocks > 0x7fffffffLL) return kInvalidArgument;
-  rope_kv_write_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+  NormRopeParams np;
+  np.r = p;
+  np.q_weight = np.k_weight = nullptr; np.eps = 0.f; np.unit_offset = 0;
+  return launch_rope<false>(np, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mvb_qk_norm_rope_kv_write(void* q, int64_t q_row_stride, void* k, int64_t k_row_stride, const void* v,
@@ -288,10 +276,5 @@ extern "C" int mvb_qk_norm_rope_kv_write(void* q, int64_t q_row_stride, void* k,
   np.q_weight = static_cast<const __nv_bfloat16*>(q_weight);
   np.k_weight = static_cast<const __nv_bfloat16*>(k_weight);
   np.eps = eps; np.unit_offset = unit_offset;
-  const int64_t tasks = static_cast<int64_t>(num_q_heads + num_kv_heads) * pph + static_cast<int64_t>(num_kv_heads) * head_dim / 8;
-  if (tasks % pph != 0) return kUnsupportedShape;
-  const int64_t blocks = (tasks * num_tokens + 255) / 256;
-  if (blocks > 0x7fffffffLL) return kInvalidArgument;
-  qk_norm_rope_kv_write_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(np);
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+  return launch_rope<true>(np, static_cast<cudaStream_t>(stream));
 }

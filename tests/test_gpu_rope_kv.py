@@ -35,11 +35,14 @@ def test_rope_matches_reference_golden(cuda, name):
     assert torch.equal(bits(k), torch.from_numpy(z[f"{name}/k_out"]))
 
 
-@pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (4, 1, 256), (2, 2, 64)])
-def test_fused_write_bit_exact_with_strided_qkv(cuda, hq, hkv, d):
+# (the kernel gives a warp 1, 2 or 5 groups of 32 tasks depending on the token count: 301 / 1200 / 3000 tokens of
+# the Qwen3 shape and 2500 of the Gemma3 shape cover the three variants)
+@pytest.mark.parametrize("hq,hkv,d,T", [(16, 8, 128, 301), (4, 1, 256, 301), (2, 2, 64, 301), (16, 8, 128, 1200),
+                                        (16, 8, 128, 3000), (4, 1, 256, 2500), (3, 1, 48, 700)])
+def test_fused_write_bit_exact_with_strided_qkv(cuda, hq, hkv, d, T):
     """q/k/v are column slices of one packed GEMM output (row stride != heads*dim), some slots are -1."""
     g = generator(11)
-    T, nblk, bs = 301, 6, 256
+    nblk, bs = -(-T // 256) + 4, 256
     max_pos = 2048
     table = rope_kv.cos_sin_table(d, max_pos, 1e6)
     qkv = randn_bf16(g, T, (hq + 2 * hkv) * d)
@@ -98,11 +101,13 @@ def test_out_of_range_slot_and_position_are_reported(cuda):
     assert status[0].item() == 3 and status[1].item() == 3
 
 
-@pytest.mark.parametrize("hq,hkv,d,unit_offset", [(16, 8, 128, False), (4, 1, 256, True), (8, 2, 128, True)])
-def test_fused_qk_norm_rope_write_matches_unfused_sequence(cuda, hq, hkv, d, unit_offset):
+@pytest.mark.parametrize("hq,hkv,d,unit_offset,T", [(16, 8, 128, False, 257), (4, 1, 256, True, 257), (8, 2, 128, True, 257),
+                                                    (16, 8, 128, False, 1100), (16, 8, 128, False, 2600),
+                                                    (4, 1, 256, True, 2400)])
+def test_fused_qk_norm_rope_write_matches_unfused_sequence(cuda, hq, hkv, d, unit_offset, T):
     """norm -> bf16 -> RoPE -> cache, fused: equal to the oracle up to the summation order of the squares."""
     g = generator(21)
-    T, nblk, bs, max_pos, eps = 257, 4, 256, 4096, 1e-6
+    nblk, bs, max_pos, eps = -(-T // 256) + 3, 256, 4096, 1e-6
     table = rope_kv.cos_sin_table(d, max_pos, 1e6)
     qkv = randn_bf16(g, T, (hq + 2 * hkv) * d) * 3
     qw, kw = randn_bf16(g, d) * 0.5 + (0 if unit_offset else 1), randn_bf16(g, d) * 0.5 + (0 if unit_offset else 1)
