@@ -252,7 +252,15 @@ int mvb_sample(const void* logits, int64_t row_stride, int num_rows, int vocab, 
  *     out = rmsnorm(x, weight)     (the following input / post-attention / pre-feedforward / final norm)
  *   rmsnorm(v, w) = v * rsqrt(mean(v^2) + eps) * w, or * (1 + w) when unit_offset != 0, in fp32.
  *   hidden must be a multiple of 8 and at most 8192.
+ * mvb_add_rmsnorm_last_tokens: the same residual add and norm, but only for the LAST token of every sequence of
+ *   a packed prefill batch, gathered by the kernel itself: output row r is computed from source row
+ *   cu_seqlens_q[r + 1] - 1, which is the row the reference picks with last_indices = cu_seqlens_q[1:] - 1
+ *   (minivllm/models/models/qwen3.py:215-217, gemma3.py:258-260) AFTER running the final norm over every token.
+ *   x is read only (the residual stream is not needed after the final norm); out is [num_seqs, hidden].
  */
+int mvb_add_rmsnorm_last_tokens(const void* x, const void* y, int64_t y_row_stride, const void* y_weight,
+                                const void* weight, void* out, const int32_t* cu_seqlens_q, int num_seqs, int hidden,
+                                float eps, int unit_offset, void* stream);
 int mvb_act_mul(const void* gate_up, int64_t in_row_stride, void* out, int64_t out_row_stride, int rows,
                 int intermediate, int gelu_tanh, void* stream);
 int mvb_add_rmsnorm(void* x, const void* y, int64_t y_row_stride, const void* y_weight, const void* weight,

@@ -64,9 +64,14 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16
                                                                   const __nv_bfloat16* __restrict__ y_weight,
                                                                   const __nv_bfloat16* __restrict__ weight,
                                                                   __nv_bfloat16* __restrict__ out, int hidden,
-                                                                  float eps, int unit_offset) {
+                                                                  float eps, int unit_offset,
+                                                                  const int32_t* __restrict__ row_ends) {
   __shared__ float scratch[kNormThreads / 32];
-  const int row = blockIdx.x;
+  // row_ends != nullptr: output row r is computed from source row row_ends[r + 1] - 1 (the last token of
+  // sequence r of a packed prefill batch) and the residual stream is left as it is
+  const int out_row = blockIdx.x;
+  const int row = row_ends != nullptr ? row_ends[out_row + 1] - 1 : out_row;
+  if (row < 0) return;                                       // (an empty batch prefix: nothing to read)
   const int nvec = hidden / 8;
   const float one = unit_offset ? 1.f : 0.f;
   float xv[VPT][8];
@@ -113,7 +118,7 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16
         ra[i] = pack_bf16(bf16_lo(ra[i]) + xv[k][2 * i], bf16_hi(ra[i]) + xv[k][2 * i + 1]);
         xv[k][2 * i] = bf16_lo(ra[i]); xv[k][2 * i + 1] = bf16_hi(ra[i]);
       }
-      *reinterpret_cast<uint4*>(x + static_cast<int64_t>(row) * hidden + v * 8) = rv;
+      if (row_ends == nullptr) *reinterpret_cast<uint4*>(x + static_cast<int64_t>(row) * hidden + v * 8) = rv;
 #pragma unroll
       for (int i = 0; i < 8; ++i) ss += xv[k][i] * xv[k][i];
     }
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16
 #pragma unroll
       for (int i = 0; i < 4; ++i)
         oa[i] = pack_bf16(xv[k][2 * i] * rstd * (one + bf16_lo(wa[i])), xv[k][2 * i + 1] * rstd * (one + bf16_hi(wa[i])));
-      *reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * hidden + v * 8) = ov;
+      *reinterpret_cast<uint4*>(out + static_cast<int64_t>(out_row) * hidden + v * 8) = ov;
     }
   }
 }
@@ -154,8 +159,9 @@ extern "C" int mvb_act_mul(const void* gate_up, int64_t in_row_stride, void* out
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
-extern "C" int mvb_add_rmsnorm(void* x, const void* y, int64_t y_row_stride, const void* y_weight, const void* weight,
-                               void* out, int rows, int hidden, float eps, int unit_offset, void* stream) {
+static int add_rmsnorm_impl(void* x, const void* y, int64_t y_row_stride, const void* y_weight, const void* weight,
+                            void* out, const int32_t* row_ends, int rows, int hidden, float eps, int unit_offset,
+                            void* stream) {
   using namespace mvb;
   if (!x || !y || !weight || !out || rows < 0 || hidden <= 0) return kInvalidArgument;
   if (hidden % 8 || y_row_stride % 8 || !a16(x) || !a16(y) || !a16(weight) || !a16(out) || !a16(y_weight)) return kMisaligned;
@@ -168,8 +174,21 @@ extern "C" int mvb_add_rmsnorm(void* x, const void* y, int64_t y_row_stride, con
   auto* op = static_cast<__nv_bfloat16*>(out);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int vpt = (hidden / 8 + kNormThreads - 1) / kNormThreads;
-  if (vpt <= 1) add_rmsnorm_kernel<1><<<rows, kNormThreads, 0, st>>>(xp, yp, y_row_stride, ywp, wp, op, hidden, eps, unit_offset);
-  else if (vpt == 2) add_rmsnorm_kernel<2><<<rows, kNormThreads, 0, st>>>(xp, yp, y_row_stride, ywp, wp, op, hidden, eps, unit_offset);
-  else add_rmsnorm_kernel<4><<<rows, kNormThreads, 0, st>>>(xp, yp, y_row_stride, ywp, wp, op, hidden, eps, unit_offset);
+  if (vpt <= 1) add_rmsnorm_kernel<1><<<rows, kNormThreads, 0, st>>>(xp, yp, y_row_stride, ywp, wp, op, hidden, eps, unit_offset, row_ends);
+  else if (vpt == 2) add_rmsnorm_kernel<2><<<rows, kNormThreads, 0, st>>>(xp, yp, y_row_stride, ywp, wp, op, hidden, eps, unit_offset, row_ends);
+  else add_rmsnorm_kernel<4><<<rows, kNormThreads, 0, st>>>(xp, yp, y_row_stride, ywp, wp, op, hidden, eps, unit_offset, row_ends);
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+extern "C" int mvb_add_rmsnorm(void* x, const void* y, int64_t y_row_stride, const void* y_weight, const void* weight,
+                               void* out, int rows, int hidden, float eps, int unit_offset, void* stream) {
+  return add_rmsnorm_impl(x, y, y_row_stride, y_weight, weight, out, nullptr, rows, hidden, eps, unit_offset, stream);
+}
+
+extern "C" int mvb_add_rmsnorm_last_tokens(const void* x, const void* y, int64_t y_row_stride, const void* y_weight,
+                                           const void* weight, void* out, const int32_t* cu_seqlens_q, int num_seqs,
+                                           int hidden, float eps, int unit_offset, void* stream) {
+  if (!cu_seqlens_q) return mvb::kInvalidArgument;
+  return add_rmsnorm_impl(const_cast<void*>(x), y, y_row_stride, y_weight, weight, out, cu_seqlens_q, num_seqs, hidden,
+                          eps, unit_offset, stream);
 }

@@ -69,7 +69,12 @@ struct PrefillCfg {
   // warpgroups (two idle warps) so that registers can be handed from that last warpgroup to the softmax ones.
   static constexpr bool REBALANCE = SPLIT > 1;
   static constexpr int THREADS = SM_WARPS * 32 + (REBALANCE ? 128 : 64);
-  static constexpr int REGS_SOFTMAX = 112, REGS_OTHER = 64;
+  // What setmaxnreg can hand around is what the block was given at launch: THREADS x the launch count
+  // (65536 / THREADS rounded down to a multiple of 8).  An increase beyond that pool would wait forever.
+  static constexpr int REGS_LAUNCH = (65536 / THREADS) / 8 * 8;
+  static constexpr int REGS_SOFTMAX = 104, REGS_OTHER = 64;
+  static_assert(!REBALANCE || SM_WARPS * 32 * REGS_SOFTMAX + 128 * REGS_OTHER <= THREADS * REGS_LAUNCH,
+                "register budgets exceed the pool of the launch");
   static constexpr int KH = BN / SPLIT;                // keys of a tile per softmax thread
   static constexpr int NCHT = KH / 32;                 // 32-key chunks per softmax thread
   static constexpr int DH = D / SPLIT;                 // columns of O per softmax thread

@@ -7,14 +7,16 @@
 // Random: keep every entry >= the k-th largest, then the nucleus of probability mass top_p among those, then
 // argmax over the kept entries of  logit / T - log(-log(u)),  u from Philox4x32-10 with
 // counter (column/4, row, offset_lo, offset_hi), key (seed_lo, seed_hi), word column%4.
-//   Usual case (0 < k < vocab and the k-th largest lies within one binade of the maximum): each CTA streams its
-//   slice once for the maximum (DRAM), the cluster agrees on the row maximum, each CTA streams its slice again
-//   (L2) and moves the entries within 127 bf16 steps of the maximum - about 1 % of a row - into the first CTA's
-//   shared memory.  There the k-th key, the nucleus and the draw are found on that short list: its keys take
-//   only 128 distinct values, so ONE 128-bin count gives the k-th key exactly, and a bin's probability mass is
-//   its count times the weight of its value (no floating-point atomics).
-//   Otherwise (no top-k, a very peaked row, NaNs): the first CTA radix-selects over the whole row with two
-//   256-bin histogram passes (and two more of softmax mass for the nucleus).
+//   Usual case (0 < k <= 1024 < vocab): each CTA streams its slice once (DRAM) keeping, per thread, the maxima of
+//   two interleaved subsets of what it reads - 1024 sub-maxima per CTA.  Their k-th largest is a value that at
+//   least k entries of the slice reach, so every entry of the row's top k that lies in this slice reaches it too.
+//   The CTA streams its slice again (L2) and moves the entries that reach it - about k of them - into the first
+//   CTA's shared memory.  There, on a list of a few hundred entries at most, each entry counts the entries
+//   larger than itself (its rank, for top-k) and their probability mass (for the nucleus): no sort, no
+//   histogram, no floating-point atomics.
+//   Otherwise (no top-k, k beyond the sub-maxima, NaNs, a list too long to rank pairwise): the first CTA
+//   radix-selects with two 256-bin histogram passes (and two more of softmax mass for the nucleus), over the
+//   list if it has one, else over the whole row.
 #include "common.cuh"
 #include "host_util.cuh"
 #include "mini_vllm_b200.h"
@@ -286,6 +288,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_greedy_kernel(const Sam
 }
 
 constexpr int kKeptCap = 4096;       // kept (top-k) entries that the random path holds in shared memory
+constexpr int kRankCap = 1024;       // lists up to this length are ranked by pairwise comparison
 
 __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(const SampleParams p) {
   namespace cg = cooperative_groups;
@@ -300,7 +303,7 @@ __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(c
   __shared__ int32_t kept_col[kKeptCap];
   __shared__ uint16_t kept_bits[kKeptCap];
   __shared__ uint32_t n_kept_s;
-  __shared__ uint32_t slice_max_s;                           // largest key of this CTA's slice (read by the cluster)
+  __shared__ float kept_w[kRankCap];                         // softmax weights of a short list
   const int r = blockIdx.x / parts;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint16_t* row = p.logits + r * p.row_stride;
@@ -324,38 +327,70 @@ __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(c
     return __fsub_rn(x, logf(-logf(u)));
   };
 
-  // ---- the usual case: the k-th largest lies within one binade of the row maximum ------------------------
+  // ---- the usual case: a short list that is sure to hold the row's top k ---------------------------------------
   // (the whole cluster sees the same k, so either every CTA takes this branch or only the first one goes on)
   const bool windowed = k > 0 && k < p.vocab;
   if (!windowed && part != 0) return;
+  bool have_list = false;                                    // the first CTA's list holds at least k entries, among them the top k
   if (windowed) {
-    // 1. the row maximum: packed bf16 compares, 1-2 instructions per two logits; a NaN poisons the maximum,
-    //    which empties the window below and sends the row down the general way
+    // The first CTA's list counter starts at zero before any CTA of the cluster adds to it: everybody arrives
+    // on the cluster barrier here (the first CTA after the store) and waits only when it is about to touch the
+    // first CTA's shared memory, much later.
+    if (threadIdx.x == 0) n_kept_s = 0;
+    if (parts > 1) {
+      __syncthreads();
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    }
+    // 1. per thread the maxima of the even and of the odd columns it reads (packed bf16 compares, 1-2
+    //    instructions per two logits)
     __nv_bfloat162 m2 = __floats2bfloat162_rn(-INFINITY, -INFINITY);
     for_each_word_slice(row, p.vocab, vec_ok, part, parts,
                         [&](int, uint32_t w) { m2 = __hmax2_nan(m2, *reinterpret_cast<const __nv_bfloat162*>(&w)); });
-    const __nv_bfloat16 m1 = __hmax_nan(__low2bfloat16(m2), __high2bfloat16(m2));
-    uint32_t kmax = __reduce_max_sync(0xffffffffu, sort_key(__bfloat16_as_ushort(m1)));
-    if (lane == 0) hist[warp] = kmax;
-    if (threadIdx.x == 0) n_kept_s = 0;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-      const uint32_t m = __reduce_max_sync(0xffffffffu, threadIdx.x < NW ? hist[threadIdx.x] : 0u);
-      if (threadIdx.x == 0) slice_max_s = m;
-    }
-    cluster.sync();                                          // every slice maximum is published
-    if (threadIdx.x < 32) {
-      uint32_t m = 0;
-      if (threadIdx.x < parts) m = *cluster.map_shared_rank(&slice_max_s, threadIdx.x);
-      m = __reduce_max_sync(0xffffffffu, m);
-      if (threadIdx.x == 0) sel_s[0] = m;
-    }
-    __syncthreads();
-    kmax = sel_s[0];
-    // 2. everything within 127 bf16 steps of the maximum goes into this CTA's list ...
-    {
-      const uint32_t lo = kmax > 127u ? kmax - 127u : 0u;
-      const __nv_bfloat16 t1 = __ushort_as_bfloat16(key_to_bits(lo));
+    // 2. the k-th largest of the CTA's 2 * kSampleThreads sub-maxima, by two radix passes over their 16-bit keys.
+    //    A NaN (its key lies above +inf's) or a k beyond the number of sub-maxima sends the row the general way.
+    const uint32_t key_lo = sort_key(__bfloat16_as_ushort(__low2bfloat16(m2)));
+    const uint32_t key_hi = sort_key(__bfloat16_as_ushort(__high2bfloat16(m2)));
+    const bool odd = (key_lo > 0xff80u) || (key_hi > 0xff80u) || k > 2 * kSampleThreads;
+    // the bin (counted from the top) in which the running count reaches `need`, and what is still needed inside it
+    auto pick_bin = [&](uint32_t need) {                       // warp 0; result in sel_s
+      uint32_t c[8], mine = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { c[j] = hist[255 - 8 * lane - j]; mine += c[j]; }
+      uint32_t incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      const uint32_t first = __ffs(__ballot_sync(0xffffffffu, incl >= need)) - 1;   // need <= total: some lane qualifies
+      if (lane == static_cast<int>(first)) {
+        uint32_t left = need - (incl - mine);
+        int j = 0;
+        while (j < 7 && c[j] < left) { left -= c[j]; ++j; }
+        sel_s[0] = 255 - 8 * lane - j; sel_s[1] = left;
+      }
+    };
+    for (int i = threadIdx.x; i < 256; i += kSampleThreads) hist[i] = 0;
+    const bool any_odd = __syncthreads_or(odd);
+    uint32_t cut = 0;                                          // the slice's entries with key >= cut go on the list
+    if (!any_odd) {
+      atomicAdd(&hist[key_lo >> 8], 1u);
+      atomicAdd(&hist[key_hi >> 8], 1u);
+      __syncthreads();
+      if (warp == 0) pick_bin(static_cast<uint32_t>(k));
+      __syncthreads();
+      const uint32_t hi_bin = sel_s[0], need_hi = sel_s[1];
+      for (int i = threadIdx.x; i < 256; i += kSampleThreads) hist[i] = 0;
+      __syncthreads();
+      if ((key_lo >> 8) == hi_bin) atomicAdd(&hist[key_lo & 0xffu], 1u);
+      if ((key_hi >> 8) == hi_bin) atomicAdd(&hist[key_hi & 0xffu], 1u);
+      __syncthreads();
+      if (warp == 0) pick_bin(need_hi);
+      __syncthreads();
+      cut = (hi_bin << 8) | sel_s[0];
+      __syncthreads();                                         // sel_s is free again
+      // 3. the entries that reach the cut go into this CTA's list ...
+      const __nv_bfloat16 t1 = __ushort_as_bfloat16(key_to_bits(cut));
       const __nv_bfloat162 t2 = __halves2bfloat162(t1, t1);
       auto push = [&](int c, uint16_t bits) {
         if (c >= p.vocab) return;                             // the pad of an odd last column
@@ -369,102 +404,105 @@ __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(c
         if (ge >> 16) push(c + 1, static_cast<uint16_t>(w >> 16));
       });
     }
-    // 3. ... and from there into the first CTA's list, one reservation per CTA
+    __syncthreads();
+    // 4. ... and from there into the first CTA's list, one reservation per CTA (a CTA that could not make a
+    //    list reserves more than the list can hold, which sends the row the general way)
     if (parts > 1) {
-      __syncthreads();
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
       if (part != 0) {
-        const uint32_t n_local = n_kept_s;
+        const uint32_t n_local = any_odd ? kKeptCap + 1 : n_kept_s;
         uint32_t* n_remote = cluster.map_shared_rank(&n_kept_s, 0);
         int32_t* col_remote = cluster.map_shared_rank(kept_col, 0);
         uint16_t* bits_remote = cluster.map_shared_rank(kept_bits, 0);
         if (threadIdx.x == 0) sel_s[1] = atomicAdd(n_remote, n_local);
         __syncthreads();
         const uint32_t base = sel_s[1];
-        for (uint32_t i = threadIdx.x; i < n_local && i < kKeptCap; i += kSampleThreads) {
-          const uint32_t slot = base + i;
-          if (slot < kKeptCap) { col_remote[slot] = kept_col[i]; bits_remote[slot] = kept_bits[i]; }
+        if (!any_odd) {
+          for (uint32_t i = threadIdx.x; i < n_local && i < kKeptCap; i += kSampleThreads) {
+            const uint32_t slot = base + i;
+            if (slot < kKeptCap) { col_remote[slot] = kept_col[i]; bits_remote[slot] = kept_bits[i]; }
+          }
         }
+      } else if (any_odd && threadIdx.x == 0) {
+        atomicAdd(&n_kept_s, kKeptCap + 1);
       }
       cluster.sync();                                        // the first CTA's list is complete; the others are done
       if (part != 0) return;
-    } else {
+    } else if (any_odd) {
+      if (threadIdx.x == 0) n_kept_s = kKeptCap + 1;
       __syncthreads();
     }
     const uint32_t n = n_kept_s;
-    if (n >= static_cast<uint32_t>(k) && n <= kKeptCap) {
-      // 4. the list's keys are kmax - 0 .. kmax - 127: one count per distance from the maximum
-      for (int i = threadIdx.x; i < 128; i += kSampleThreads) hist[i] = 0;
+    have_list = n >= static_cast<uint32_t>(k) && n <= kKeptCap;
+    if (have_list && n <= kRankCap) {
+      // 5. ranks and masses by pairwise comparison.  Keys replace the raw bits (-0 becomes +0: same value).
+      uint32_t km = 0;
+      for (uint32_t i = threadIdx.x; i < n; i += kSampleThreads) {
+        const uint32_t key = sort_key(kept_bits[i]);
+        kept_bits[i] = static_cast<uint16_t>(key);
+        km = key > km ? key : km;
+      }
+      km = __reduce_max_sync(0xffffffffu, km);
+      if (lane == 0) hist[warp] = km;
       __syncthreads();
-      for (uint32_t i = threadIdx.x; i < n; i += kSampleThreads) atomicAdd(&hist[kmax - sort_key(kept_bits[i])], 1u);
-      __syncthreads();
-      if (warp == 0) {
-        // lane owns distances 4 * lane .. 4 * lane + 3 (ascending distance = descending value)
-        uint32_t cnt[4], mine = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { cnt[j] = hist[4 * lane + j]; mine += cnt[j]; }
-        uint32_t incl = mine;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += up;
-        }
-        uint32_t cum = incl - mine, kth = 128;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          cum += cnt[j];
-          if (kth == 128 && cum >= static_cast<uint32_t>(k)) kth = 4 * lane + j;
-        }
-        kth = __reduce_min_sync(0xffffffffu, kth);           // distance of the k-th largest (n >= k: it exists)
-        if (top_p < 1.f) {
-          // nucleus among the kept: a bin's mass is its count times exp(value / T - max / T)
-          float xmax = bits_to_float(key_to_bits(kmax));
-          if (scaled) xmax = __fdiv_rn(xmax, temp);
-          float m[4], msum = 0.f;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t dist = 4 * lane + j;
-            m[j] = 0.f;
-            if (cnt[j] != 0u && dist <= kth) {
-              float x = bits_to_float(key_to_bits(kmax - dist));
-              if (scaled) x = __fdiv_rn(x, temp);
-              m[j] = static_cast<float>(cnt[j]) * expf(x - xmax);
-            }
-            msum += m[j];
-          }
-          float mincl = msum;
-#pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const float up = __shfl_up_sync(0xffffffffu, mincl, o);
-            if (lane >= o) mincl += up;
-          }
-          const float need = top_p * __shfl_sync(0xffffffffu, mincl, 31);
-          float mc = mincl - msum;
-          uint32_t cut = 128;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            mc += m[j];
-            if (cut == 128 && m[j] > 0.f && mc >= need) cut = 4 * lane + j;
-          }
-          cut = __reduce_min_sync(0xffffffffu, cut);
-          kth = cut < kth ? cut : kth;
-        }
-        if (lane == 0) sel_s[0] = kth;
+      if (threadIdx.x < 32) {
+        const uint32_t m = __reduce_max_sync(0xffffffffu, threadIdx.x < NW ? hist[threadIdx.x] : 0u);
+        if (threadIdx.x == 0) sel_s[0] = m;
       }
       __syncthreads();
-      const uint32_t max_dist = sel_s[0];
-      Best b{-INFINITY, 0x7fffffff};
+      float xmax = bits_to_float(key_to_bits(sel_s[0]));
+      if (scaled) xmax = __fdiv_rn(xmax, temp);
       for (uint32_t i = threadIdx.x; i < n; i += kSampleThreads) {
-        const uint16_t bits = kept_bits[i];
-        if (kmax - sort_key(bits) > max_dist) continue;
-        const int c = kept_col[i];
-        const float score = gumbel_score(c, bits);
-        if (better(score, c, b.val, b.idx)) { b.val = score; b.idx = c; }
+        float x = bits_to_float(key_to_bits(kept_bits[i]));
+        if (scaled) x = __fdiv_rn(x, temp);
+        kept_w[i] = expf(x - xmax);
+      }
+      __syncthreads();
+      // entry i stays in the top k iff fewer than k entries are larger; it stays in the nucleus iff the mass of
+      // the larger entries is below top_p of the kept mass (entries equal to the last one admitted stay too)
+      constexpr int PER = (kRankCap + kSampleThreads - 1) / kSampleThreads;
+      uint32_t cnt[PER];
+      float above[PER], kept_mass = 0.f;
+#pragma unroll
+      for (int u = 0; u < PER; ++u) {
+        const uint32_t i = threadIdx.x + u * kSampleThreads;
+        cnt[u] = 0; above[u] = 0.f;
+        if (i < n) {
+          const uint32_t key = kept_bits[i];
+          for (uint32_t j = 0; j < n; ++j) {
+            const bool larger = kept_bits[j] > key;
+            cnt[u] += larger ? 1u : 0u;
+            above[u] += larger ? kept_w[j] : 0.f;
+          }
+          if (cnt[u] < static_cast<uint32_t>(k)) kept_mass += kept_w[i];
+        }
+      }
+      float need = INFINITY;
+      if (top_p < 1.f) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) kept_mass += __shfl_xor_sync(0xffffffffu, kept_mass, o);
+        if (lane == 0) mass[warp] = kept_mass;
+        __syncthreads();
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) total += mass[w];
+        need = top_p * total;
+      }
+      Best b{-INFINITY, 0x7fffffff};
+#pragma unroll
+      for (int u = 0; u < PER; ++u) {
+        const uint32_t i = threadIdx.x + u * kSampleThreads;
+        if (i < n && cnt[u] < static_cast<uint32_t>(k) && (above[u] < need || cnt[u] == 0u)) {
+          const int c = kept_col[i];
+          const float score = gumbel_score(c, key_to_bits(kept_bits[i]));
+          if (better(score, c, b.val, b.idx)) { b.val = score; b.idx = c; }
+        }
       }
       b = block_argmax(b);
       if (threadIdx.x == 0) emit(b.idx);
       return;
     }
-    __syncthreads();                                         // the list is of no use: the general way, from scratch
+    __syncthreads();
   }
 
   // ---- the general way: radix selection over the whole row (first CTA of the cluster only) -----------------
@@ -534,7 +572,10 @@ __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(c
 
   uint32_t thresh = 0;                                       // keep keys >= thresh
   bool compact = false;                                      // the candidates sit in shared memory
-  if (windowed) {
+  if (windowed && have_list) {
+    thresh = kth_key(true);                                  // (a list too long to rank pairwise)
+    compact = true;
+  } else if (windowed) {
     // the kept entries (k of them, plus ties at the threshold) into shared memory if they fit
     thresh = kth_key(false);
     gather(thresh);

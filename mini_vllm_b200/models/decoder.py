@@ -94,20 +94,27 @@ class DecoderLayer(nn.Module):
             self.pre_feedforward_layernorm, self.post_feedforward_layernorm = norm(), norm()
 
     def forward(self, ctx: Context, x: torch.Tensor, h: torch.Tensor, positions: torch.Tensor,
-                next_norm: RMSNorm) -> torch.Tensor:
+                next_norm: RMSNorm, last_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """``x`` is the residual stream (updated in place), ``h`` its already normalised copy for this
         layer; returns the normalised input of the next layer (``next_norm`` applied to the new ``x``).
         Each residual add is fused with the norm that follows it (and, for Gemma, with the norm on the
-        branch output), which is the reference's dataflow (qwen3.py:146-155, gemma3.py:157-170)."""
+        branch output), which is the reference's dataflow (qwen3.py:146-155, gemma3.py:157-170).
+
+        ``last_tokens`` (the batch's ``cu_seqlens_q``, last layer of a prefill only): the closing add and the
+        final norm are computed for the last token of every sequence alone - the rows the lm_head reads
+        (qwen3.py:215-217) - gathered inside the kernel; the result has one row per sequence."""
         a = self.self_attn(ctx, h, positions)
+        post_mlp = None if not self.gemma else self.post_feedforward_layernorm.weight
         if not self.gemma:
             n = self.post_attention_layernorm
             h = ops.add_rmsnorm(x, a, n.weight, n.eps, False)
-            return ops.add_rmsnorm(x, self.mlp(h), next_norm.weight, next_norm.eps, False)
-        n = self.pre_feedforward_layernorm
-        h = ops.add_rmsnorm(x, a, n.weight, n.eps, True, y_weight=self.post_attention_layernorm.weight)
-        return ops.add_rmsnorm(x, self.mlp(h), next_norm.weight, next_norm.eps, True,
-                               y_weight=self.post_feedforward_layernorm.weight)
+        else:
+            n = self.pre_feedforward_layernorm
+            h = ops.add_rmsnorm(x, a, n.weight, n.eps, True, y_weight=self.post_attention_layernorm.weight)
+        if last_tokens is not None:
+            return ops.add_rmsnorm_last_tokens(x, self.mlp(h), next_norm.weight, next_norm.eps, self.gemma, last_tokens,
+                                               y_weight=post_mlp)
+        return ops.add_rmsnorm(x, self.mlp(h), next_norm.weight, next_norm.eps, self.gemma, y_weight=post_mlp)
 
 
 class DecoderLM(nn.Module):
@@ -149,13 +156,13 @@ class DecoderLM(nn.Module):
             x = x * self.embed_scale.to(x.dtype)
         x = x.contiguous()
         h = self.layers[0].input_layernorm(x)
+        last = len(self.layers) - 1
         for i, layer in enumerate(self.layers):
-            nxt = self.layers[i + 1].input_layernorm if i + 1 < len(self.layers) else self.norm
-            h = layer(ctx, x, h, positions, nxt)
-        x = h                                                  # the final norm is already applied
-        if ctx.prefill:
-            x = x[ctx.cu_seqlens_q[1:] - 1].contiguous()
-        return self.lm_head(x)
+            nxt = self.layers[i + 1].input_layernorm if i < last else self.norm
+            # at prefill the lm_head reads one row per sequence: the last layer's closing add + final norm gather
+            # those rows themselves instead of normalising every token and indexing afterwards
+            h = layer(ctx, x, h, positions, nxt, ctx.cu_seqlens_q if (i == last and ctx.prefill) else None)
+        return self.lm_head(h)                                 # the final norm is already applied
 
     # ---- weights ---------------------------------------------------------------------------------
     @torch.no_grad()

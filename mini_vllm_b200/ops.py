@@ -344,3 +344,20 @@ def add_rmsnorm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: flo
     _cabi.check(rc, "mvb_add_rmsnorm")
     LaunchCounter.add(1)
     return out
+
+
+def add_rmsnorm_last_tokens(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, unit_offset: bool,
+                            cu_seqlens_q: torch.Tensor, y_weight: torch.Tensor | None = None) -> torch.Tensor:
+    """``rmsnorm(x + y)`` (or ``x + rmsnorm(y, y_weight)``) for the last token of every sequence only:
+    ``[num_seqs, hidden]``, row r from source row ``cu_seqlens_q[r + 1] - 1``.  ``x`` is left untouched."""
+    _need(x, torch.bfloat16, "x"); _need(y, torch.bfloat16, "y"); _need(weight, torch.bfloat16, "weight")
+    _need(cu_seqlens_q, torch.int32, "cu_seqlens_q")
+    assert x.dim() == 2 and x.is_contiguous() and y.shape == x.shape and y.stride(1) == 1
+    num_seqs, hidden = cu_seqlens_q.numel() - 1, x.shape[1]
+    out = torch.empty(num_seqs, hidden, dtype=torch.bfloat16, device=x.device)
+    rc = _cabi.load().mvb_add_rmsnorm_last_tokens(_ptr(x), _ptr(y), y.stride(0), _ptr(y_weight), _ptr(weight), _ptr(out),
+                                                  _ptr(cu_seqlens_q), num_seqs, hidden, float(eps),
+                                                  1 if unit_offset else 0, _stream())
+    _cabi.check(rc, "mvb_add_rmsnorm_last_tokens")
+    LaunchCounter.add(1)
+    return out

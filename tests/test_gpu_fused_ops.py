@@ -50,3 +50,23 @@ def test_add_rmsnorm(cuda, rows, hidden, unit_offset, branch_norm):
     torch.cuda.synchronize()
     close(xd, x_want, "residual")
     close(out, out_want, "norm")
+
+
+@pytest.mark.parametrize("hidden,unit_offset,branch_norm", [(1024, False, False), (1152, True, True)])
+def test_add_rmsnorm_last_tokens_is_the_gathered_full_result(cuda, hidden, unit_offset, branch_norm):
+    """The last-token variant equals running the full kernel over every row and indexing cu_seqlens_q[1:] - 1
+    afterwards (what the reference does, qwen3.py:215-217), bit for bit, and leaves the residual stream alone."""
+    g = generator(hidden)
+    lens = [5, 1, 300, 64, 17]
+    T = sum(lens)
+    x, y = (randn_bf16(g, T, hidden) * 3).to(cuda), randn_bf16(g, T, hidden).to(cuda)
+    w = (randn_bf16(g, hidden) * 0.3 + (0 if unit_offset else 1)).to(cuda)
+    yw = (randn_bf16(g, hidden) * 0.3).to(cuda) if branch_norm else None
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device=cuda)
+    x_before = x.clone()
+    got = ops.add_rmsnorm_last_tokens(x, y, w, 1e-6, unit_offset, cu, y_weight=yw)
+    assert torch.equal(x, x_before)
+    full = ops.add_rmsnorm(x.clone(), y, w, 1e-6, unit_offset, y_weight=yw)
+    want = full[(cu[1:] - 1).long()]
+    assert got.shape == (len(lens), hidden)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
