@@ -18,14 +18,11 @@
 //                   straight from the TMA layout.  The two query tiles are interleaved
 //                   (S0, PV1, S1, PV0, ...) so the tensor pipe works on one tile while the other
 //                   tile's softmax runs;
-//   softmax groups  per query tile SPLIT warpgroups, SPLIT threads per row (warp w of a group owns tensor
-//                   memory lanes 32 * (w % 4), so warps w and w + 4 see the same rows and take one half of
-//                   the keys each): tcgen05.ld brings the thread's part of the row of S into registers (no
-//                   shuffles), the partners exchange their maxima through shared memory, running max /
-//                   sum, exp2, P back to tensor memory, O rescaled in tensor memory only when the running
-//                   max moved by more than 2^8 (the stale max is carried exactly through P and the row
-//                   sum), and the epilogue O / l -> bf16 -> global.  Two threads per row halve the serial
-//                   part of a tile's softmax, which is what the S -> softmax -> P V chain of a tile waits for.
+//   softmax groups  one warpgroup per query tile, one thread per row: tcgen05.ld brings the row of
+//                   S into registers (no shuffles), running max / sum, exp2, P back to tensor
+//                   memory, O rescaled in tensor memory only when the running max moved by more
+//                   than 2^8 (the stale max is carried exactly through P and the row sum), and the
+//                   epilogue O / l -> bf16 -> global.
 // Every barrier is used round after round across items; each role keeps its own counters and derives
 // the parity it waits for from them.  Every mbarrier wait is bounded; a wait that gives up poisons
 // the CTA, which then drains (and stops taking items).
@@ -60,46 +57,27 @@ struct PrefillParams {
 // half starts while the second half is still being exponentiated.
 enum : int { B_QFULL = 0, B_KFULL = 2, B_VFULL = 4, B_KFREE = 6, B_VFREE = 8, B_SFULL = 10, B_PFULL = 12,
              B_ODONE = 16, B_OFREE = 18, B_VFIXED = 20, B_QFREE = 22, B_ITEM_FULL = 23, B_ITEM_FREE = 25,
-             B_CLC = 27, B_XCH = 28 /* one per (query tile, lane quadrant): partner warps meet here */, B_COUNT = 36 };
+             B_CLC = 27, B_COUNT = 28 };
 
-template <int D, int BN, int NQ, int SPLIT>
+template <int D, int BN, int NQ>
 struct PrefillCfg {
-  static constexpr int SM_WARPS = NQ * 4 * SPLIT;      // softmax warps: tile t owns warps t * 4 * SPLIT ...
-  // ... then the producer warp and the MMA warp.  With two threads per row the block is padded to whole
-  // warpgroups (two idle warps) so that registers can be handed from that last warpgroup to the softmax ones.
-  static constexpr bool REBALANCE = SPLIT > 1;
-  static constexpr int THREADS = SM_WARPS * 32 + (REBALANCE ? 128 : 64);
-  // What setmaxnreg can hand around is what the block was given at launch: THREADS x the launch count
-  // (65536 / THREADS rounded down to a multiple of 8).  An increase beyond that pool would wait forever.
-  static constexpr int REGS_LAUNCH = (65536 / THREADS) / 8 * 8;
-  static constexpr int REGS_SOFTMAX = 104, REGS_OTHER = 64;
-  static_assert(!REBALANCE || SM_WARPS * 32 * REGS_SOFTMAX + 128 * REGS_OTHER <= THREADS * REGS_LAUNCH,
-                "register budgets exceed the pool of the launch");
-  static constexpr int KH = BN / SPLIT;                // keys of a tile per softmax thread
-  static constexpr int NCHT = KH / 32;                 // 32-key chunks per softmax thread
-  static constexpr int DH = D / SPLIT;                 // columns of O per softmax thread
+  static constexpr int THREADS = NQ * 128 + 64;
   static constexpr int Q_BYTES = 128 * D * 2;          // one query tile
   static constexpr int KV_BYTES = BN * D * 2;          // one K (or V) tile
   static constexpr int HALF_Q = 128 * 128;             // bytes of one 64-column half of a Q tile
   static constexpr int HALF_KV = BN * 128;             // bytes of one 64-column half of K / V
-  // P is published in 64-key halves; the warps that hold keys of a half each arrive once on it
-  static constexpr int PF_COUNT = 4 * (KH >= 64 ? 1 : 64 / KH);
   // after the tiles: barriers, the tensor-memory address, the failure flag, two item slots and the
-  // launch-control response; then the partners' exchange slots and the output staging
+  // launch-control response
   static constexpr int CTRL_BYTES = 512;
-  static constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_FAIL = OFF_TMEM_SLOT + 4, OFF_ITEMS = 304, OFF_CLC = 336;
-  static constexpr int XCH_BYTES = SPLIT > 1 ? 2 * NQ * SPLIT * 128 * 4 : 0;   // [parity][tile][part][row] floats
-  static constexpr int STAGE_WARP = 1024;              // a 32-row x 32-byte output staging tile per softmax warp
-  static constexpr int STAGE_BYTES = SM_WARPS * STAGE_WARP;
-  static constexpr int SMEM = NQ * Q_BYTES + 4 * KV_BYTES + 1024 /*align*/ + CTRL_BYTES + XCH_BYTES + STAGE_BYTES;
+  static constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_FAIL = OFF_TMEM_SLOT + 4, OFF_ITEMS = 240, OFF_CLC = 272;
+  static constexpr int STAGE_BYTES = NQ * 4 * 4096;     // a 32-row x 128-byte output staging tile per softmax warp
+  static constexpr int SMEM = NQ * Q_BYTES + 4 * KV_BYTES + 1024 /*align*/ + CTRL_BYTES + STAGE_BYTES;
   static constexpr int TMEM_COLS = NQ * (BN + D) <= 256 ? 256 : 512;   // power of two
   static constexpr int S_COL = 0;                      // S_t at S_COL + t * BN (P_t aliases its first BN/2 columns)
   static constexpr int O_COL = NQ * BN;                // O_t at O_COL + t * D
   static_assert(NQ * (BN + D) <= 512, "tensor memory budget");
   static_assert(BN % 64 == 0, "P is written in 64-key halves");
-  static_assert(KH % 32 == 0 && DH % 16 == 0 && (SPLIT == 1 || SPLIT == 2), "a softmax thread works in 32-key chunks");
-  static_assert(OFF_FAIL + 4 <= OFF_ITEMS && OFF_ITEMS + 32 <= OFF_CLC && OFF_CLC + 16 <= CTRL_BYTES, "control block layout");
-  static_assert(SMEM <= 227 * 1024, "shared memory budget");
+  static_assert(OFF_FAIL + 4 <= OFF_ITEMS && OFF_CLC + 16 <= CTRL_BYTES, "control block layout");
 };
 
 // What every role derives from an item's block index.
@@ -149,11 +127,11 @@ struct PrefillItem {
   }
 };
 
-template <int D, int BN, int NQ, int SPLIT>
-__global__ void __launch_bounds__(PrefillCfg<D, BN, NQ, SPLIT>::THREADS, 1)
+template <int D, int BN, int NQ>
+__global__ void __launch_bounds__(PrefillCfg<D, BN, NQ>::THREADS, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const PrefillParams p) {
-  using C = PrefillCfg<D, BN, NQ, SPLIT>;
+  using C = PrefillCfg<D, BN, NQ>;
   using Item = PrefillItem<BN, NQ>;
   constexpr uint32_t IDESC_S = umma_idesc_bf16(128, BN, false, false);
   constexpr uint32_t IDESC_O = umma_idesc_bf16(128, D, false, true);
@@ -179,22 +157,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   volatile uint32_t* fail_flag = reinterpret_cast<uint32_t*>(ctrl + C::OFF_FAIL);
   volatile int4* items = reinterpret_cast<volatile int4*>(ctrl + C::OFF_ITEMS);   // {x, y, z, valid}
   const uint32_t clc_resp = smem_u32(ctrl + C::OFF_CLC);
-  float* xch = reinterpret_cast<float*>(ctrl + C::CTRL_BYTES);
-  const uint32_t stage_s = smem_u32(ctrl + C::CTRL_BYTES + C::XCH_BYTES);
+  const uint32_t stage_s = smem_u32(ctrl + C::CTRL_BYTES);
 
   if (tid == 0) {
     for (int i = 0; i < B_COUNT; ++i) {
       uint32_t count = 1u;
-      if (i >= B_PFULL && i < B_PFULL + 4) count = C::PF_COUNT; // one lane per softmax warp that holds keys of the half
-      if (i >= B_OFREE && i < B_OFREE + 2) count = 4u * SPLIT;
-      if (i >= B_ITEM_FREE && i < B_ITEM_FREE + 2) count = 1u + C::SM_WARPS * 32u;
-      if (i >= B_XCH && i < B_XCH + 8) count = 64u;             // the two partner warps, every thread
+      if (i >= B_PFULL && i < B_PFULL + 4) count = 4u;          // one lane per softmax warp
+      if (i >= B_OFREE && i < B_OFREE + 2) count = 4u;
+      if (i >= B_ITEM_FREE && i < B_ITEM_FREE + 2) count = 1u + NQ * 128u;
       mbar_init(&bars[i], count);
     }
     *fail_flag = 0;
     fence_mbar_init();
   }
-  if (warp == C::SM_WARPS + 1) {                              // the MMA warp owns the tensor memory
+  if (warp == NQ * 4 + 1) {                                   // the MMA warp owns the tensor memory
     tmem_alloc(tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -224,13 +200,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     return true;
   };
 
-  // Register budgets per role: the launch gives every thread the same number; the last warpgroup (producer,
-  // MMA issuer, two idle warps) hands most of its share to the softmax warpgroups, which hold their part of a
-  // row of S in registers.  (Each role adjusts its own budget first thing in its branch.)
-  auto fewer_registers = [] { if constexpr (C::REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REGS_OTHER)); };
-  auto more_registers = [] { if constexpr (C::REBALANCE) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::REGS_SOFTMAX)); };
-  if (warp >= C::SM_WARPS) fewer_registers();                 // the whole last warpgroup, before its warps part ways
-  if (warp == C::SM_WARPS) {
+  if (warp == NQ * 4) {
     // ============================ producer warp ======================================================
     // All lanes walk the items together (the zero fill is warp-wide); lane 0 owns barriers and TMA.
     Item item;
@@ -362,7 +332,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         if (v_issued >= back) mbar_wait(&bars[B_VFULL + ((v_issued - back) & 1)], ((v_issued - back) >> 1) & 1);
       }
     }
-  } else if (warp == C::SM_WARPS + 1) {
+  } else if (warp == NQ * 4 + 1) {
     // ============================ MMA warp (one issuing thread) ======================================
     // This thread shares its scheduler with two softmax warps that always have work, so every
     // instruction between two tcgen05.mma costs tensor-pipe time: ranges are scalars, tile indices
@@ -479,40 +449,24 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       }
     }
     __syncwarp();
-  } else if (warp < C::SM_WARPS) {
-    // ============================ softmax warps of query tile t =========================================
-    more_registers();
-    const int t = warp / (4 * SPLIT);
-    const int part = (warp / 4) % SPLIT;                      // which KH keys of a tile (and DH columns of O) are mine
-    const int quad = warp & 3;                                // my 32 lanes of tensor memory = rows 32 * quad ...
-    const int row = quad * 32 + lane;                         // row of the tile = TMEM lane
-    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+  } else {
+    // ============================ softmax warpgroup of query tile t ==================================
+    const int t = warp >> 2;
+    const int row = tid & 127;                                // row of the tile = TMEM lane
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const uint32_t s_addr = lane_addr + C::S_COL + t * BN;
-    const uint32_t o_addr = lane_addr + C::O_COL + t * D + part * C::DH;
-    const int key0 = part * C::KH;                            // my first key inside a tile
-    uint32_t n_s = 0, n_epi = 0, n_x = 0;                     // S tiles consumed, epilogues done, exchanges done
+    const uint32_t o_addr = lane_addr + C::O_COL + t * D;
+    uint32_t n_s = 0, n_epi = 0;                              // S tiles consumed (S / P parity), epilogues done (O parity)
     bool ok = true;
     Item item;
-    // The partner (the other part of the same rows) and I publish one float each and read the other's:
-    // slots are double-buffered by the exchange count, so a slot is rewritten only after the partner has
-    // passed the following exchange, i.e. has read it.
-    auto exchange = [&](float mine, int where) -> float {
-      if constexpr (SPLIT == 1) return mine;
-      float* slot = xch + (((n_x & 1) * NQ + t) * SPLIT) * 128;
-      slot[part * 128 + row] = mine;
-      mbar_arrive(&bars[B_XCH + t * 4 + quad]);
-      if (!wait(B_XCH + t * 4 + quad, n_x & 1, where)) { ok = false; return mine; }
-      ++n_x;
-      return slot[(part ^ 1) * 128 + row];
-    };
     for (uint32_t n_item = 0; ok && next_item(n_item, item); ++n_item) {
       // this group's tile, picked with selects so the item stays in registers
-      int rows_me = item.rows[0], pf_me = item.pf[0], jlo_me = item.jlo[0], jhi_me = item.jhi[0],
+      int rows_me = item.rows[0], pf_me = item.pf[0], pl_me = item.pl[0], jlo_me = item.jlo[0], jhi_me = item.jhi[0],
           roff_me = item.roff[0], head_me = item.head[0];
 #pragma unroll
       for (int u = 1; u < NQ; ++u)
         if (t == u) {
-          rows_me = item.rows[u]; pf_me = item.pf[u]; jlo_me = item.jlo[u]; jhi_me = item.jhi[u];
+          rows_me = item.rows[u]; pf_me = item.pf[u]; pl_me = item.pl[u]; jlo_me = item.jlo[u]; jhi_me = item.jhi[u];
           roff_me = item.roff[u]; head_me = item.head[u];
         }
       if (rows_me <= 0) continue;
@@ -541,70 +495,63 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           const int lo = max(vis_lo - cb, 0), hi = min(vis_hi - cb, 31);
           return hi < lo ? 0u : ((0xffffffffu >> (31 - hi)) & (0xffffffffu << lo));
         };
-        // My part of the row comes into registers once - one wait for all the loads, so their latency is
-        // paid once per tile - and stays there for both passes.
-        uint32_t sreg[C::NCHT][32];
-        int cls[C::NCHT];
-#pragma unroll
-        for (int c = 0; c < C::NCHT; ++c) {
-          cls[c] = chunk_class(key0 + c * 32);
-          if (cls[c] != 2) tmem_ld_32x32(s_addr + key0 + c * 32, sreg[c]);
-        }
-        tmem_wait_ld();
-        float max0 = -INFINITY, max1 = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < C::NCHT; ++c) {
-          if (cls[c] == 1) {                                      // the diagonal, the window's edge: mask in registers
-            const uint32_t bits = visible_bits(key0 + c * 32);
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (!((bits >> i) & 1u)) sreg[c][i] = 0xff800000u;  // -inf
+        // Two bodies.  Tiles that every row of the warp sees completely (the common case) bring the
+        // thread's whole row of S into registers once - one wait for all the loads, so their latency is
+        // paid once per tile - and keep it there for both passes, with no mask code at all.  The other
+        // tiles (the diagonal, the window's edge) go chunk by chunk and read S twice.
+        float sum0 = 0.f, sum1 = 0.f, alpha = 1.f, m_use = m_run;
+        constexpr int NCH = BN / 32;
+        // new running maximum (lazy: keep the old one unless the tile's is more than 2^8 larger) and the
+        // rescale of O that goes with it; S_t(itt) complete implies PV_t(itt-1) complete (one thread
+        // issues both, in order), so O is ours
+        auto new_max = [&](float tile_max) {
+          tile_max *= p.scale_log2;                           // scale > 0, so max commutes with it
+          if (tile_max > m_run + 8.f || (m_run == -INFINITY && tile_max > -INFINITY)) {
+            m_use = tile_max;
+            alpha = fast_exp2(m_run - m_use);                 // m_run = -inf -> 0
           }
-          if (cls[c] != 2) {
+          if (itt > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+            for (int c = 0; c < D / 16; ++c) {                // rare: small chunks, to stay short of registers
+              uint32_t r[16];
+              tmem_ld_32x16(o_addr + c * 16, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x16(o_addr + c * 16, r);
+            }
+          }
+        };
+        // P = exp2(S * scale - m) as packed bf16 over the first BN/2 columns of S (keys c*32 + i, i+1 ->
+        // word c*16 + i/2), written per 32 keys and published per 64 by one lane per warp
+        auto publish_p = [&](int c, const uint32_t (&pk)[16]) {
+          tmem_st_32x16(s_addr + c * 16, pk);
+          if (c & 1) {
+            tmem_wait_st();                                   // warp-wide: every lane's words are in tensor memory
+            if (lane == 0) {
+              tc_fence_before();
+              mbar_arrive(&bars[B_PFULL + 2 * t + (c >> 1)]);
+            }
+          }
+        };
+        if (w_hi >= BN - 1 && w_lo + 31 <= 0) {
+          uint32_t sreg[NCH][32];
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) tmem_ld_32x32(s_addr + c * 32, sreg[c]);
+          tmem_wait_ld();
+          float max0 = -INFINITY, max1 = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
               max0 = fmax3(max0, __uint_as_float(sreg[c][i]), __uint_as_float(sreg[c][i + 1]));
               max1 = fmax3(max1, __uint_as_float(sreg[c][i + 2]), __uint_as_float(sreg[c][i + 3]));
             }
-          }
-        }
-        // every load of S has completed on both sides of the exchange before anyone overwrites S with P
-        float tile_max = exchange(fmaxf(max0, max1), 710);
-        if (!ok) break;
-        tile_max = fmaxf(tile_max, fmaxf(max0, max1));
-        // new running maximum (lazy: keep the old one unless the tile's is more than 2^8 larger) and the
-        // rescale of my columns of O that goes with it; S_t(itt) complete implies PV_t(itt-1) complete (one
-        // thread issues both, in order), so O is ours.  Both partners see the same maxima and decide alike.
-        float alpha = 1.f, m_use = m_run;
-        tile_max *= p.scale_log2;                             // scale > 0, so max commutes with it
-        if (tile_max > m_run + 8.f || (m_run == -INFINITY && tile_max > -INFINITY)) {
-          m_use = tile_max;
-          alpha = fast_exp2(m_run - m_use);                   // m_run = -inf -> 0
-        }
-        if (itt > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-          for (int c = 0; c < C::DH / 16; ++c) {              // rare: small chunks, to stay short of registers
-            uint32_t r[16];
-            tmem_ld_32x16(o_addr + c * 16, r);
-            tmem_wait_ld();
+          new_max(fmaxf(max0, max1));
+          const float m_safe = m_use == -INFINITY ? 0.f : m_use;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x16(o_addr + c * 16, r);
-          }
-        }
-        const float m_safe = m_use == -INFINITY ? 0.f : m_use;
-        // P = exp2(S * scale - m) as packed bf16 over the first BN/2 columns of S (keys g*32 + i, i+1 ->
-        // word g*16 + i/2), written per 32 keys; a 64-key half is published by one lane of every warp that
-        // holds keys of it, after the warp's last store to it
-        float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-        for (int c = 0; c < C::NCHT; ++c) {
-          const int g = key0 / 32 + c;                        // chunk index inside the tile
-          uint32_t (&pk)[16] = *reinterpret_cast<uint32_t(*)[16]>(&sreg[c][0]);   // packed in place: word i/2 <- keys i, i+1
-          if (cls[c] == 2) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) pk[i] = 0u;
-          } else {
+          for (int c = 0; c < NCH; ++c) {
+            uint32_t pk[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
               const float e0 = fast_exp2(fmaf(__uint_as_float(sreg[c][i]), p.scale_log2, -m_safe));
@@ -612,73 +559,119 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
               sum0 += e0; sum1 += e1;
               pk[i >> 1] = pack_bf16(e0, e1);
             }
+            publish_p(c, pk);
           }
-          tmem_st_32x16(s_addr + g * 16, pk);
-          if ((g & 1) || c == C::NCHT - 1) {
-            tmem_wait_st();                                   // warp-wide: every lane's words are in tensor memory
-            if (lane == 0) {
-              tc_fence_before();
-              mbar_arrive(&bars[B_PFULL + 2 * t + (g >> 1)]);
+        } else {
+          // chunks every row of the warp sees completely run the plain code here too
+          float tile_max = -INFINITY;
+#pragma unroll 1
+          for (int c = 0; c < NCH; ++c) {
+            const int cl = chunk_class(c * 32);
+            if (cl == 2) continue;
+            uint32_t r[32];
+            tmem_ld_32x32(s_addr + c * 32, r);
+            tmem_wait_ld();
+            if (cl == 0) {
+              float max0 = -INFINITY, max1 = -INFINITY;
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                max0 = fmax3(max0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                max1 = fmax3(max1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+              }
+              tile_max = fmax3(tile_max, max0, max1);
+            } else {
+              const uint32_t bits = visible_bits(c * 32);
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                tile_max = fmaxf(tile_max, (bits >> i) & 1u ? __uint_as_float(r[i]) : -INFINITY);
             }
+          }
+          new_max(tile_max);
+          const float m_safe = m_use == -INFINITY ? 0.f : m_use;
+#pragma unroll 1
+          for (int c = 0; c < NCH; ++c) {
+            uint32_t pk[16];
+            const int cl = chunk_class(c * 32);
+            if (cl == 2) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pk[i] = 0u;
+            } else {
+              uint32_t r[32];
+              tmem_ld_32x32(s_addr + c * 32, r);
+              tmem_wait_ld();
+              if (cl == 1) {
+                const uint32_t bits = visible_bits(c * 32);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (!((bits >> i) & 1u)) r[i] = 0xff800000u;  // -inf
+              }
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float e0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_safe));
+                const float e1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_safe));
+                sum0 += e0; sum1 += e1;
+                pk[i >> 1] = pack_bf16(e0, e1);
+              }
+            }
+            publish_p(c, pk);
           }
         }
         l_run = l_run * alpha + (sum0 + sum1);
         m_run = m_use;
       }
       // ---- epilogue: while it runs, the other roles are already at work on the next item ------------
-      if (ok) l_run += SPLIT > 1 ? exchange(l_run, 720) : 0.f;    // the row sum is the partners' sums together
       if (ok) ok = wait(B_ODONE + t, n_epi & 1, 800);
       ++n_epi;
       if (ok) {
         tc_fence_after();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        // A thread owns a row, so storing from registers would touch 32 lines per instruction.  Each warp
-        // turns its 32 rows through a 1 KB staging tile, 16 columns (32 bytes a row) at a time, with the
-        // 16-byte units of two neighbouring rows interleaved by the row's parity (conflict-free both ways),
-        // and writes whole 32-byte sectors.  My columns of O come out of tensor memory 32 at a time; after
-        // the last load O_t belongs to the next item.
-        const uint32_t stage = stage_s + warp * C::STAGE_WARP;
-        const int wrow0 = quad * 32;
-        __nv_bfloat16* obase = p.out + (static_cast<int64_t>(item.q0) + item.row0 + roff_me + wrow0) * p.out_stride +
-                               static_cast<int64_t>(head_me) * D + part * C::DH;
-#pragma unroll 1
-        for (int c = 0; c < C::DH / 32; ++c) {
+        // the whole row of O, normalised, as bf16 pairs in registers; then O_t belongs to the next item
+        uint32_t packed[D / 2];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(o_addr + c * 32, r);
           tmem_wait_ld();
-          if (c == C::DH / 32 - 1 && lane == 0) {             // the wait above is warp-wide
-            tc_fence_before();
-            mbar_arrive(&bars[B_OFREE + t]);
-          }
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            r[i] = pack_bf16(__uint_as_float(r[2 * i]) * inv, __uint_as_float(r[2 * i + 1]) * inv);
+            packed[c * 16 + i] = pack_bf16(__uint_as_float(r[2 * i]) * inv, __uint_as_float(r[2 * i + 1]) * inv);
+        }
+        if (lane == 0) {                                      // the wait above is warp-wide
+          tc_fence_before();
+          mbar_arrive(&bars[B_OFREE + t]);
+        }
+        // A thread owns a row, so storing from registers would touch 32 lines per instruction.  Each
+        // warp turns its 32 rows through a 4 KB staging tile (16-byte units XOR-swizzled by the row,
+        // conflict-free both ways) and writes whole 128-byte lines, 64 columns at a time.
+        const uint32_t stage = stage_s + warp * 4096;
+        const int wrow0 = (warp & 3) * 32;
+        __nv_bfloat16* obase = p.out + (static_cast<int64_t>(item.q0) + item.row0 + roff_me + wrow0) * p.out_stride +
+                               static_cast<int64_t>(head_me) * D;
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < D / 64; ++h) {
 #pragma unroll
-            for (int u = 0; u < 2; ++u)
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 32 + ((u ^ ((lane >> 2) & 1)) << 4)),
-                           "r"(r[h * 8 + u * 4]), "r"(r[h * 8 + u * 4 + 1]), "r"(r[h * 8 + u * 4 + 2]),
-                           "r"(r[h * 8 + u * 4 + 3]) : "memory");
-            __syncwarp();
+          for (int u = 0; u < 8; ++u)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 128 + ((u ^ (lane & 7)) << 4)),
+                         "r"(packed[h * 32 + u * 4]), "r"(packed[h * 32 + u * 4 + 1]), "r"(packed[h * 32 + u * 4 + 2]),
+                         "r"(packed[h * 32 + u * 4 + 3]) : "memory");
+          __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              const int rr = i * 16 + (lane >> 1), un = lane & 1;
-              uint4 w;
-              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
-                           : "r"(stage + rr * 32 + ((un ^ ((rr >> 2) & 1)) << 4)) : "memory");
-              if (wrow0 + rr < rows_me)
-                *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(rr) * p.out_stride + c * 32 + h * 16 + un * 8) = w;
-            }
-            __syncwarp();
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3), un = lane & 7;
+            uint4 w;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                         : "r"(stage + rr * 128 + ((un ^ (rr & 7)) << 4)) : "memory");
+            if (wrow0 + rr < rows_me)
+              *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(rr) * p.out_stride + h * 64 + un * 8) = w;
           }
+          __syncwarp();
         }
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == C::SM_WARPS + 1) tmem_dealloc(tmem, C::TMEM_COLS);
+  if (warp == NQ * 4 + 1) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
 struct PrefillOperands {            // what the tensor maps are built from
@@ -687,9 +680,9 @@ struct PrefillOperands {            // what the tensor maps are built from
   int total_q, hq, hkv;
 };
 
-template <int D, int BN, int NQ, int SPLIT>
+template <int D, int BN, int NQ>
 static int launch_prefill(const PrefillOperands& op, const PrefillParams& p, int max_seqlen_q, cudaStream_t stream) {
-  using C = PrefillCfg<D, BN, NQ, SPLIT>;
+  using C = PrefillCfg<D, BN, NQ>;
   if (p.block_table != nullptr && p.block_size % BN != 0) return kUnsupportedShape;   // a KV tile must not straddle blocks
   // the TMA boxes are tied to the kernel's tile sizes: 128 query rows, BN key rows
   CUtensorMap qm, km, vm;
@@ -699,14 +692,14 @@ static int launch_prefill(const PrefillOperands& op, const PrefillParams& p, int
   if (rc != kOk) return rc;
   rc = make_kv_tensor_map(&vm, op.v, op.kv_rows, op.hkv, D, op.v_stride, BN);
   if (rc != kOk) return rc;
-  rc = opt_in_dynamic_smem<C>(reinterpret_cast<const void*>(&prefill_attn_kernel<D, BN, NQ, SPLIT>), C::SMEM);
+  rc = opt_in_dynamic_smem<C>(reinterpret_cast<const void*>(&prefill_attn_kernel<D, BN, NQ>), C::SMEM);
   if (rc != kOk) return rc;
   PrefillParams pp = p;
   pp.pair_heads = (NQ > 1 && p.group % NQ == 0) ? 1 : 0;
   const int rows_per_cta = pp.pair_heads ? 128 : 128 * NQ;
   dim3 grid(pp.pair_heads ? p.hq / NQ : p.hq, p.num_seqs, (max_seqlen_q + rows_per_cta - 1) / rows_per_cta);
   if (grid.z > 65535) return kUnsupportedShape;
-  prefill_attn_kernel<D, BN, NQ, SPLIT><<<grid, C::THREADS, C::SMEM, stream>>>(qm, km, vm, pp);
+  prefill_attn_kernel<D, BN, NQ><<<grid, C::THREADS, C::SMEM, stream>>>(qm, km, vm, pp);
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
@@ -741,6 +734,6 @@ extern "C" int mvb_prefill_attn(const void* q, int64_t q_row_stride, const void*
   p.out = static_cast<__nv_bfloat16*>(out); p.out_stride = out_row_stride;
   p.dev_status = dev_status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (head_dim == 128) return launch_prefill<128, 128, 2, 2>(op, p, max_seqlen_q, st);
-  return launch_prefill<256, 64, 1, 1>(op, p, max_seqlen_q, st);
+  if (head_dim == 128) return launch_prefill<128, 128, 2>(op, p, max_seqlen_q, st);
+  return launch_prefill<256, 64, 1>(op, p, max_seqlen_q, st);
 }

@@ -30,8 +30,11 @@ struct RopeParams {
   int* dev_status;
 };
 
-// Rounds exactly like the eager fp32 reference: each product and the sum are rounded on
-// their own (no FMA contraction), then one round-to-nearest-even to bf16.
+// EXACT rounds exactly like the eager fp32 reference: each product and the sum are rounded on their own (no FMA
+// contraction), then one round-to-nearest-even to bf16.  Without it one product of each pair is fused into
+// the sum (a third fewer instructions): the result can differ in the last fp32 bit, i.e. almost never after
+// the rounding to bf16; used where bit-exactness is not promised (the variant with the norm fused in front).
+template <bool EXACT>
 __device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float* cs, const float* sn) {
   uint32_t* a = reinterpret_cast<uint32_t*>(&lo);
   uint32_t* b = reinterpret_cast<uint32_t*>(&hi);
@@ -40,10 +43,18 @@ __device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float* cs, c
     float x1a = bf16_lo(a[i]), x1b = bf16_hi(a[i]);
     float x2a = bf16_lo(b[i]), x2b = bf16_hi(b[i]);
     float c0 = cs[2 * i], c1 = cs[2 * i + 1], s0 = sn[2 * i], s1 = sn[2 * i + 1];
-    float y1a = __fsub_rn(__fmul_rn(x1a, c0), __fmul_rn(x2a, s0));
-    float y1b = __fsub_rn(__fmul_rn(x1b, c1), __fmul_rn(x2b, s1));
-    float y2a = __fadd_rn(__fmul_rn(x2a, c0), __fmul_rn(x1a, s0));
-    float y2b = __fadd_rn(__fmul_rn(x2b, c1), __fmul_rn(x1b, s1));
+    float y1a, y1b, y2a, y2b;
+    if (EXACT) {
+      y1a = __fsub_rn(__fmul_rn(x1a, c0), __fmul_rn(x2a, s0));
+      y1b = __fsub_rn(__fmul_rn(x1b, c1), __fmul_rn(x2b, s1));
+      y2a = __fadd_rn(__fmul_rn(x2a, c0), __fmul_rn(x1a, s0));
+      y2b = __fadd_rn(__fmul_rn(x2b, c1), __fmul_rn(x1b, s1));
+    } else {
+      y1a = fmaf(x1a, c0, -__fmul_rn(x2a, s0));
+      y1b = fmaf(x1b, c1, -__fmul_rn(x2b, s1));
+      y2a = fmaf(x2a, c0, __fmul_rn(x1a, s0));
+      y2b = fmaf(x2b, c1, __fmul_rn(x1b, s1));
+    }
     a[i] = pack_bf16(y1a, y1b);
     b[i] = pack_bf16(y2a, y2b);
   }
@@ -56,7 +67,8 @@ __device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float* cs, c
 // independent 128-bit loads, plus the token's slot, position and cos/sin entries), then rotates and stores.
 // With D/16 dividing 32 a lane meets the same chunk index in every group, so its cos/sin values are loaded
 // once per token.  ITEMS is chosen on the host: large for long prefills (bytes in flight per thread bound the
-// bandwidth), 1 for decode batches (enough warps to cover the GPU matter more).
+// bandwidth), 1 for decode batches (enough warps to cover the GPU matter more).  Three blocks per SM: with
+// five groups per warp the kernel is otherwise held to two by its registers, and measured a fifth slower.
 //
 // NORM adds the per-head RMSNorm of q and k in front of the rotation: each head row is normalised in fp32
 // (y = x * rsqrt(mean(x^2) + eps) * w, or * (1 + w) for Gemma), rounded to bf16 as the separate norm kernel
@@ -71,7 +83,7 @@ struct NormRopeParams {
 };
 
 template <int ITEMS, bool NORM>
-__global__ void __launch_bounds__(256) rope_kv_kernel(const NormRopeParams np) {
+__global__ void __launch_bounds__(256, 3) rope_kv_kernel(const NormRopeParams np) {
   const RopeParams& p = np.r;
   const int pph = p.d / 16;                                  // chunk pairs per head
   const int rope_tasks = (p.hq + p.hkv) * pph;               // per token
@@ -168,7 +180,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const NormRopeParams np) {
     if (is_q && !rotate && !NORM) continue;                  // plain store_kvcache leaves q alone
     if (rotate && pos_ok) {
       if (!same_chunk) load_table(c);
-      rotate8(lo[j], hi[j], cs, sn);
+      rotate8<!NORM>(lo[j], hi[j], cs, sn);
     }
     __nv_bfloat16* row = is_q ? p.q + t * p.q_stride + head * p.d : p.k + t * p.k_stride + (head - p.hq) * p.d;
     if ((is_q || p.k_in_place) && (rotate || NORM)) {

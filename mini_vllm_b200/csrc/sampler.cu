@@ -304,6 +304,7 @@ __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(c
   __shared__ uint16_t kept_bits[kKeptCap];
   __shared__ uint32_t n_kept_s;
   __shared__ float kept_w[kRankCap];                         // softmax weights of a short list
+  __shared__ uint32_t cut_s;                                 // this slice's cut (read by the cluster)
   const int r = blockIdx.x / parts;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint16_t* row = p.logits + r * p.row_stride;
@@ -333,14 +334,7 @@ __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(c
   if (!windowed && part != 0) return;
   bool have_list = false;                                    // the first CTA's list holds at least k entries, among them the top k
   if (windowed) {
-    // The first CTA's list counter starts at zero before any CTA of the cluster adds to it: everybody arrives
-    // on the cluster barrier here (the first CTA after the store) and waits only when it is about to touch the
-    // first CTA's shared memory, much later.
-    if (threadIdx.x == 0) n_kept_s = 0;
-    if (parts > 1) {
-      __syncthreads();
-      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    }
+    if (threadIdx.x == 0) n_kept_s = 0;                        // (visible to the cluster before anybody adds to it: sync below)
     // 1. per thread the maxima of the even and of the odd columns it reads (packed bf16 compares, 1-2
     //    instructions per two logits)
     __nv_bfloat162 m2 = __floats2bfloat162_rn(-INFINITY, -INFINITY);
@@ -372,7 +366,7 @@ __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(c
     };
     for (int i = threadIdx.x; i < 256; i += kSampleThreads) hist[i] = 0;
     const bool any_odd = __syncthreads_or(odd);
-    uint32_t cut = 0;                                          // the slice's entries with key >= cut go on the list
+    uint32_t cut = 0;                                          // entries with key >= cut go on the list
     if (!any_odd) {
       atomicAdd(&hist[key_lo >> 8], 1u);
       atomicAdd(&hist[key_hi >> 8], 1u);
@@ -389,6 +383,24 @@ __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(c
       __syncthreads();
       cut = (hi_bin << 8) | sel_s[0];
       __syncthreads();                                         // sel_s is free again
+    }
+    // The row has at least k entries that reach ANY slice's cut, so the largest of the cuts serves every slice
+    // and the lists of all slices together hold about k entries instead of k per slice.
+    if (parts > 1) {
+      if (threadIdx.x == 0) cut_s = any_odd ? 0xffffffffu : cut;
+      cluster.sync();
+      if (threadIdx.x < 32) {
+        uint32_t c = 0;
+        if (threadIdx.x < parts) c = *cluster.map_shared_rank(&cut_s, threadIdx.x);
+        c = __reduce_max_sync(0xffffffffu, c);
+        if (threadIdx.x == 0) sel_s[0] = c;
+      }
+      __syncthreads();
+      cut = sel_s[0];
+      __syncthreads();
+    }
+    const bool give_up = parts > 1 ? cut == 0xffffffffu : any_odd;   // some slice could not make a cut: the general way
+    if (!give_up) {
       // 3. the entries that reach the cut go into this CTA's list ...
       const __nv_bfloat16 t1 = __ushort_as_bfloat16(key_to_bits(cut));
       const __nv_bfloat162 t2 = __halves2bfloat162(t1, t1);
@@ -405,35 +417,26 @@ __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(c
       });
     }
     __syncthreads();
-    // 4. ... and from there into the first CTA's list, one reservation per CTA (a CTA that could not make a
-    //    list reserves more than the list can hold, which sends the row the general way)
+    // 4. ... and from there into the first CTA's list, one reservation per CTA
     if (parts > 1) {
-      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-      if (part != 0) {
-        const uint32_t n_local = any_odd ? kKeptCap + 1 : n_kept_s;
+      if (part != 0 && !give_up) {
+        const uint32_t n_local = n_kept_s;
         uint32_t* n_remote = cluster.map_shared_rank(&n_kept_s, 0);
         int32_t* col_remote = cluster.map_shared_rank(kept_col, 0);
         uint16_t* bits_remote = cluster.map_shared_rank(kept_bits, 0);
         if (threadIdx.x == 0) sel_s[1] = atomicAdd(n_remote, n_local);
         __syncthreads();
         const uint32_t base = sel_s[1];
-        if (!any_odd) {
-          for (uint32_t i = threadIdx.x; i < n_local && i < kKeptCap; i += kSampleThreads) {
-            const uint32_t slot = base + i;
-            if (slot < kKeptCap) { col_remote[slot] = kept_col[i]; bits_remote[slot] = kept_bits[i]; }
-          }
+        for (uint32_t i = threadIdx.x; i < n_local && i < kKeptCap; i += kSampleThreads) {
+          const uint32_t slot = base + i;
+          if (slot < kKeptCap) { col_remote[slot] = kept_col[i]; bits_remote[slot] = kept_bits[i]; }
         }
-      } else if (any_odd && threadIdx.x == 0) {
-        atomicAdd(&n_kept_s, kKeptCap + 1);
       }
       cluster.sync();                                        // the first CTA's list is complete; the others are done
       if (part != 0) return;
-    } else if (any_odd) {
-      if (threadIdx.x == 0) n_kept_s = kKeptCap + 1;
-      __syncthreads();
     }
     const uint32_t n = n_kept_s;
-    have_list = n >= static_cast<uint32_t>(k) && n <= kKeptCap;
+    have_list = !give_up && n >= static_cast<uint32_t>(k) && n <= kKeptCap;
     if (have_list && n <= kRankCap) {
       // 5. ranks and masses by pairwise comparison.  Keys replace the raw bits (-0 becomes +0: same value).
       uint32_t km = 0;
