@@ -236,7 +236,7 @@ def decode_roofline(engine, contexts, peaks):
             "note": "algorithmic K+V bytes of recorded decode steps, 28 layer launches replayed from a CUDA graph; peak = STREAM copy"}
 
 
-LEGS = ("attn3", "prefill", "attn4", "sampler", "rope", "pack")
+LEGS = ("attn3", "prefill", "attn4", "sampler", "rope", "pack", "head")
 
 
 def graph_time_ms(sweep, launches_per_sweep: int, reps: int = 5) -> float:
@@ -311,6 +311,34 @@ def rope_and_pack_legs(dev, peaks, legs) -> dict:
     return out
 
 
+def head_legs(dev, peaks) -> dict:
+    """lm_head + greedy sampling on Qwen3's head (hidden 1024, vocabulary 151 936): the fused kernel against the
+    cuBLAS GEMM followed by the greedy sampler.  The floor of either is reading the 311 MB weight matrix once."""
+    from mini_vllm_b200 import ops
+    out = {}
+    hidden, vocab = 1024, 151936
+    ws = [(torch.randn(vocab, hidden, device=dev) * 0.02).to(torch.bfloat16) for _ in range(2)]   # 2 x 311 MB > L2
+    for rows in (512, 64):
+        xs = [torch.randn(rows, hidden, device=dev).to(torch.bfloat16) for _ in range(2)]
+        scratch = ops.lm_head_argmax_scratch(rows, dev)
+        tok = torch.empty(rows, dtype=torch.int64, device=dev)
+        logits = torch.empty(rows, vocab, dtype=torch.bfloat16, device=dev)
+        flops, w_bytes = 2 * rows * hidden * vocab, vocab * hidden * 2
+
+        def unfused():
+            for x, w in zip(xs, ws):
+                torch.matmul(x, w.t(), out=logits)
+                ops.sample(logits, out=tok)
+        ms_fused = graph_time_ms(lambda: [ops.lm_head_argmax(x, w, scratch, out=tok) for x, w in zip(xs, ws)], 2)
+        ms_unfused = graph_time_ms(unfused, 2)
+        out[f"lm_head_argmax_{rows}"] = {"us": round(ms_fused * 1e3, 1), "unfused_us": round(ms_unfused * 1e3, 1),
+                                         "TFLOP/s": round(flops / ms_fused / 1e9, 1),
+                                         "weight_GB/s": round(w_bytes / ms_fused / 1e6, 1),
+                                         "frac_of_measured_bf16": round(flops / ms_fused / 1e9 / peaks["bf16_tflops"], 4),
+                                         "frac_of_measured_hbm": round(w_bytes / ms_fused / 1e6 / peaks["hbm_gbs"], 4)}
+    return out
+
+
 def kernel_extras(dev, peaks, nl=4, legs=LEGS):
     """Fixed single-layer cases: the 240-sequence decode batch and the 16-sequence prefill batch.
 
@@ -324,6 +352,8 @@ def kernel_extras(dev, peaks, nl=4, legs=LEGS):
     if "sampler" in legs:
         out.update(sampler_legs(dev, peaks))
     out.update(rope_and_pack_legs(dev, peaks, legs))
+    if "head" in legs:
+        out.update(head_legs(dev, peaks))
     return out
 
 

@@ -238,6 +238,29 @@ int mvb_sample(const void* logits, int64_t row_stride, int num_rows, int vocab, 
                int64_t* scatter_table, const int32_t* scatter_index, int32_t* dev_status, void* stream);
 
 /*
+ * lm_head and greedy sampling in one kernel: out[r] = argmax_n bf16(sum_k hidden_states[r, k] * weight[n, k]),
+ * the lowest column winning ties.
+ * Replaces, for requests without top-k / top-p (the reference's argmax path), logits = lm_head(hidden_states)
+ * (minivllm/models/models/qwen3.py:215-219, gemma3.py:258-262) followed by Sampler.forward's
+ * torch.argmax (minivllm/models/layers/sampler.py:31): a tcgen05 GEMM whose epilogue rounds each accumulator to
+ * bf16 - the logit the unfused path would have stored - and keeps only the best (value, column) per row, so the
+ * [num_rows, vocab] logits are never written or read back.  A positive temperature does not change an argmax
+ * and is not needed here.
+ *   hidden_states [num_rows, hidden] bf16 (row stride in elements), weight [vocab, hidden] bf16 (the lm_head /
+ *   tied embedding matrix as stored); hidden a multiple of 64; rows 16-byte aligned.
+ *   scratch: mvb_lm_head_argmax_scratch_bytes(max rows) bytes of device memory that the caller zeroes ONCE; every
+ *   call leaves it zeroed again.  Calls that share a scratch must not overlap on the GPU.
+ *   scatter_table / scatter_index as for mvb_sample.
+ * Accumulation is fp32 in the tensor cores' order, which is not cuBLAS's: a logit can round to the neighbouring
+ * bf16 value, so the token may differ from the unfused path where the two best logits are within one bf16 step.
+ */
+size_t mvb_lm_head_argmax_scratch_bytes(int max_rows);
+int mvb_lm_head_argmax(const void* hidden_states, int64_t x_row_stride, const void* weight, int64_t w_row_stride,
+                       int num_rows, int hidden, int vocab, int64_t* out, int64_t* scatter_table,
+                       const int32_t* scatter_index, void* scratch, size_t scratch_bytes, int32_t* dev_status,
+                       void* stream);
+
+/*
  * Decoder-layer glue around the attention path.  A decode step of a small model is bound by the number
  * of kernels it launches, so the elementwise chains the models run between their GEMMs are fused.
  *

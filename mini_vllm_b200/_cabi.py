@@ -34,6 +34,8 @@ SIGNATURES = {
     "mvb_act_mul": (i32, [vp, i64, vp, i64, i32, i32, i32, vp]),
     "mvb_add_rmsnorm": (i32, [vp, vp, i64, vp, vp, vp, i32, i32, f32, i32, vp]),
     "mvb_add_rmsnorm_last_tokens": (i32, [vp, vp, i64, vp, vp, vp, vp, i32, i32, f32, i32, vp]),
+    "mvb_lm_head_argmax_scratch_bytes": (sz, [i32]),
+    "mvb_lm_head_argmax": (i32, [vp, i64, vp, i64, i32, i32, i32, vp, vp, vp, vp, sz, vp, vp]),
     "mvb_sample": (i32, [vp, i64, i32, i32, vp, vp, vp, u64, u64, vp, vp, vp, vp, vp]),
 }
 

@@ -44,6 +44,9 @@ class Config:
     # unfused sequence).  False: stand-alone norms, then the RoPE + write kernel whose cache contents are
     # bit-identical to the reference's eager rotation and copy.
     fuse_qk_norm: bool = True
+    # True: a step whose requests all sample greedily (no top-k / top-p) runs lm_head and argmax as one kernel and
+    # never materialises its logits.  False: lm_head, then the sampler, as the reference does.
+    fused_greedy_head: bool = True
 
     def __post_init__(self):
         if self.hf_config is None:

@@ -18,7 +18,7 @@ PKG = CSRC.parent
 ROOT = PKG.parent
 LIB = PKG / "libmini_vllm_b200.so"
 OBJ_DIR = CSRC / "build"
-SOURCES = ["api.cu", "pack.cu", "rope_kv_write.cu", "decode_attn.cu", "prefill_attn.cu", "sampler.cu", "fused_ops.cu"]
+SOURCES = ["api.cu", "pack.cu", "rope_kv_write.cu", "decode_attn.cu", "prefill_attn.cu", "sampler.cu", "fused_ops.cu", "lm_head_argmax.cu"]
 HEADERS = ["common.cuh", "host_util.cuh", "scan.cuh", str(ROOT / "include" / "mini_vllm_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo", "--extended-lambda",
               "-Xcompiler", "-fPIC", "-I", str(ROOT / "include"), "-I", str(CSRC)]

@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_greedy_kernel(const Sam
 constexpr int kKeptCap = 4096;       // kept (top-k) entries that the random path holds in shared memory
 constexpr int kRankCap = 1024;       // lists up to this length are ranked by pairwise comparison
 
-__global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(const SampleParams p) {
+__global__ void __launch_bounds__(kSampleThreads, 3) sample_topk_gumbel_kernel(const SampleParams p) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   const int parts = static_cast<int>(cluster.num_blocks()), part = static_cast<int>(cluster.block_rank());
@@ -690,9 +690,13 @@ extern "C" int mvb_sample(const void* logits, int64_t row_stride, int num_rows, 
   SampleParams p{static_cast<const uint16_t*>(logits), row_stride, vocab, temperatures, top_k, top_p, seed, offset,
                  out, scatter_table, scatter_index};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // enough CTAs for two per SM: a cluster of up to 8 per row when the batch is small
+  // A cluster of up to 8 CTAs per row when the batch is small.  Greedy rows are one streaming pass: enough CTAs
+  // for two per SM.  The random path pays for every extra slice with a longer candidate list and two cluster
+  // barriers, so it stops splitting once half the SMs have a CTA.
+  const bool greedy = top_k == nullptr && top_p == nullptr;
+  const int64_t enough = greedy ? 2 * sm_count() : (sm_count() + 1) / 2;
   int parts = 1;
-  while (parts < 8 && static_cast<int64_t>(num_rows) * parts < 2 * sm_count()) parts *= 2;
+  while (parts < 8 && static_cast<int64_t>(num_rows) * parts < enough) parts *= 2;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(num_rows) * parts);
   cfg.blockDim = dim3(kSampleThreads);
@@ -702,7 +706,6 @@ extern "C" int mvb_sample(const void* logits, int64_t row_stride, int num_rows, 
   attr[0].val.clusterDim.x = parts; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const bool greedy = top_k == nullptr && top_p == nullptr;
   const cudaError_t err = greedy ? cudaLaunchKernelEx(&cfg, sample_greedy_kernel, p)
                                  : cudaLaunchKernelEx(&cfg, sample_topk_gumbel_kernel, p);
   return err == cudaSuccess ? kOk : kLaunchFailed;

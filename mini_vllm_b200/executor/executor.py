@@ -68,6 +68,8 @@ class Executor:
         self._step = 0
         self.token_table = torch.zeros(0, dtype=torch.int64, device=self.device)   # last token per request slot
         self._out_ring = torch.zeros(self.RING, max(config.max_num_batched_seqs, 1), dtype=torch.int64).pin_memory()
+        self.fused_head = bool(getattr(config, "fused_greedy_head", True))
+        self._head_scratch = ops.lm_head_argmax_scratch(max(config.max_num_batched_seqs, 16), self.device)
         self.h2d_bytes = 0                   # bytes uploaded by the packing path (for the bench's e2e line)
         self.d2h_bytes = 0
         self.graph_runner = None
@@ -217,6 +219,19 @@ class Executor:
         self.d2h_bytes += tokens.numel() * 8
         return tokens.tolist()
 
+    def _tokens(self, hidden_rows: torch.Tensor, requests: list[Request], scatter_table=None, scatter_index=None):
+        """The head of a step: token ids from the rows the lm_head reads.  A batch that only samples greedily (the
+        reference's argmax path, sampler.py:31; a temperature does not move an argmax) takes the fused lm_head +
+        argmax kernel; otherwise lm_head, then the sampler."""
+        temperatures, top_k, top_p = self._build_sample_input(requests)
+        rows = hidden_rows.shape[0]
+        if self.fused_head and top_k is None and top_p is None and rows * 8 + 8 <= self._head_scratch.numel():
+            return self.model.greedy_tokens(hidden_rows, self._head_scratch, scatter_table=scatter_table,
+                                            scatter_index=scatter_index, status=self.status)
+        logits = self.model.lm_head(hidden_rows)
+        return self.sampler(logits, temperatures, top_p=top_p, top_k=top_k, scatter_table=scatter_table,
+                            scatter_index=scatter_index)
+
     # ---- pipelined step: nothing comes back to the host ---------------------------------------------
     def ensure_token_table(self, num_slots: int) -> None:
         if self.token_table.numel() < num_slots:
@@ -276,10 +291,7 @@ class Executor:
                               status=self.status)
         if meta is not None:
             self.h2d_bytes += meta.numel() * 4
-        logits = self.forward(ctx, input_ids)
-        temperatures, top_k, top_p = self._build_sample_input(reqs)
-        tokens = self.sampler(logits, temperatures, top_p=top_p, top_k=top_k, scatter_table=self.token_table,
-                              scatter_index=slots_dev)
+        tokens = self._tokens(self.forward(ctx, input_ids, head=False), reqs, self.token_table, slots_dev)
         host = self._out_ring[self._step % self.RING, :b]
         host.copy_(tokens, non_blocking=True)
         self.d2h_bytes += b * 8
@@ -288,17 +300,19 @@ class Executor:
         return host, event
 
     # ---- forward ---------------------------------------------------------------------------------
-    def prefill(self, ctx: Context, input_ids: torch.Tensor) -> torch.Tensor:
-        return self.model(ctx, input_ids, ctx.positions)
+    def prefill(self, ctx: Context, input_ids: torch.Tensor, head: bool = True) -> torch.Tensor:
+        return self.model(ctx, input_ids, ctx.positions, head=head)
 
-    def decode(self, ctx: Context, input_ids: torch.Tensor) -> torch.Tensor:
+    def decode(self, ctx: Context, input_ids: torch.Tensor, head: bool = True) -> torch.Tensor:
         gr = self.graph_runner
         if gr is not None and gr.max_batch_size >= input_ids.size(0):
-            return gr.replay(ctx, input_ids)
-        return self.model(ctx, input_ids, ctx.positions)
+            rows = gr.replay(ctx, input_ids)                   # the captured step ends in front of the head
+            return self.model.lm_head(rows) if head else rows
+        return self.model(ctx, input_ids, ctx.positions, head=head)
 
-    def forward(self, ctx: Context, tokens: torch.Tensor) -> torch.Tensor:
-        return self.prefill(ctx, tokens) if ctx.prefill else self.decode(ctx, tokens)
+    def forward(self, ctx: Context, tokens: torch.Tensor, head: bool = True) -> torch.Tensor:
+        """Logits (``head=True``, the reference's contract, executor.py:197-214) or the rows the head reads."""
+        return self.prefill(ctx, tokens, head) if ctx.prefill else self.decode(ctx, tokens, head)
 
     @torch.inference_mode()
     def execute(self, batch: Batch) -> list[int]:
@@ -309,8 +323,9 @@ class Executor:
             input_ids, ctx = self._build_mixed_input(batch.requests, batch.num_decode)
         else:
             input_ids, ctx = self._build_decode_input(batch.requests)
-        logits = self.forward(ctx, input_ids)
-        return self.sample(logits, batch)
+        tokens = self._tokens(self.forward(ctx, input_ids, head=False), batch.requests)
+        self.d2h_bytes += tokens.numel() * 8
+        return tokens.tolist()
 
     def check_device_status(self) -> None:
         """Synchronising check of the kernels' error word (bad slots / block ids / positions)."""

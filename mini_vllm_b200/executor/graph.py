@@ -33,7 +33,10 @@ class CudaGraphRunner:
         self.slot_mapping = torch.full((m,), -1, dtype=torch.int32, device=dev)
         self.cache_seqlens = torch.zeros(m, dtype=torch.int32, device=dev)
         self.block_table = torch.full((m, config.kv_cache_num_blocks), -1, dtype=torch.int32, device=dev)
-        self.outputs = torch.zeros(m, config.hf_config.vocab_size, dtype=config.hf_config.dtype, device=dev)
+        # The captured step ends at the rows the lm_head reads (final norm applied); the head itself - the GEMM and
+        # the sampler, or the fused argmax kernel - runs behind the replay, where the executor knows whether the
+        # batch samples greedily.  (The reference captures the logits, graph.py:21.)
+        self.outputs = torch.zeros(m, config.hf_config.hidden_size, dtype=config.hf_config.dtype, device=dev)
 
     def padded_size(self, bs: int) -> int:
         return next(b for b in self.batch_size_list if b >= bs)
@@ -51,12 +54,12 @@ class CudaGraphRunner:
     def _capture_batch(self, bs: int) -> None:
         # one eager run first: lazy initialisation (cuBLAS handles, kernel attributes, the decode
         # workspace) must not happen inside the capture
-        self.outputs[:bs] = self.model(self.static_context(bs), self.input_ids[:bs], self.positions[:bs])
+        self.outputs[:bs] = self.model(self.static_context(bs), self.input_ids[:bs], self.positions[:bs], head=False)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         before = LaunchCounter.total
         with torch.cuda.graph(g, pool=self.pool):
-            self.outputs[:bs] = self.model(self.static_context(bs), self.input_ids[:bs], self.positions[:bs])
+            self.outputs[:bs] = self.model(self.static_context(bs), self.input_ids[:bs], self.positions[:bs], head=False)
         self.launches[bs] = LaunchCounter.total - before
         self.pool = g.pool()
         self.graphs[bs] = g
@@ -67,6 +70,7 @@ class CudaGraphRunner:
 
     @torch.inference_mode()
     def replay(self, ctx: Context, input_ids: torch.Tensor) -> torch.Tensor:
+        """Runs the captured step; returns the ``[bs, hidden]`` rows for the head."""
         bs = input_ids.size(0)
         if not self.owns(ctx):                       # foreign context: stage it like graph.py:64-70
             self.input_ids[:bs] = input_ids

@@ -150,7 +150,10 @@ class DecoderLM(nn.Module):
         if cfg.tie_word_embeddings:
             self.lm_head.weight = self.embed_tokens.weight
 
-    def forward(self, ctx: Context, input_ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx: Context, input_ids: torch.Tensor, positions: torch.Tensor, head: bool = True) -> torch.Tensor:
+        """Logits, one row per sequence (``head=True``, the reference's contract), or the rows the lm_head would
+        read - final norm applied, last token of every sequence at prefill - for a caller that runs the head
+        itself (``greedy_tokens`` or ``lm_head``)."""
         x = self.embed_tokens(input_ids)
         if self.embed_scale is not None:
             x = x * self.embed_scale.to(x.dtype)
@@ -162,7 +165,15 @@ class DecoderLM(nn.Module):
             # at prefill the lm_head reads one row per sequence: the last layer's closing add + final norm gather
             # those rows themselves instead of normalising every token and indexing afterwards
             h = layer(ctx, x, h, positions, nxt, ctx.cu_seqlens_q if (i == last and ctx.prefill) else None)
-        return self.lm_head(h)                                 # the final norm is already applied
+        return self.lm_head(h) if head else h                  # the final norm is already applied
+
+    def greedy_tokens(self, hidden_rows: torch.Tensor, scratch: torch.Tensor, out: torch.Tensor | None = None,
+                      scatter_table: torch.Tensor | None = None, scatter_index: torch.Tensor | None = None,
+                      status: torch.Tensor | None = None) -> torch.Tensor:
+        """``argmax(lm_head(hidden_rows))`` in one kernel: the logits are never written (qwen3.py:215-219 followed
+        by sampler.py:31 for requests without top-k / top-p)."""
+        return ops.lm_head_argmax(hidden_rows, self.lm_head.weight, scratch, out=out, scatter_table=scatter_table,
+                                  scatter_index=scatter_index, status=status)
 
     # ---- weights ---------------------------------------------------------------------------------
     @torch.no_grad()

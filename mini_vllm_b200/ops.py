@@ -361,3 +361,31 @@ def add_rmsnorm_last_tokens(x: torch.Tensor, y: torch.Tensor, weight: torch.Tens
     _cabi.check(rc, "mvb_add_rmsnorm_last_tokens")
     LaunchCounter.add(1)
     return out
+
+
+def lm_head_argmax_scratch(max_rows: int, device) -> torch.Tensor:
+    """Zeroed scratch for ``lm_head_argmax`` (every call leaves it zeroed again)."""
+    n = _cabi.load().mvb_lm_head_argmax_scratch_bytes(max_rows)
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def lm_head_argmax(hidden_states: torch.Tensor, weight: torch.Tensor, scratch: torch.Tensor,
+                   out: torch.Tensor | None = None, scatter_table: torch.Tensor | None = None,
+                   scatter_index: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``argmax(hidden_states @ weight.T)`` per row over bf16-rounded logits, without materialising them."""
+    _need(hidden_states, torch.bfloat16, "hidden_states"); _need(weight, torch.bfloat16, "weight")
+    assert hidden_states.dim() == 2 and weight.dim() == 2 and hidden_states.stride(1) == 1 and weight.stride(1) == 1
+    rows, hidden = hidden_states.shape
+    vocab = weight.shape[0]
+    assert weight.shape[1] == hidden
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int64, device=hidden_states.device)
+    if scatter_table is not None:
+        _need(scatter_table, torch.int64, "scatter_table"); _need(scatter_index, torch.int32, "scatter_index")
+        assert scatter_index.numel() >= rows
+    rc = _cabi.load().mvb_lm_head_argmax(_ptr(hidden_states), hidden_states.stride(0), _ptr(weight), weight.stride(0), rows,
+                                         hidden, vocab, _ptr(out), _ptr(scatter_table), _ptr(scatter_index), _ptr(scratch),
+                                         scratch.numel(), _ptr(status), _stream())
+    _cabi.check(rc, "mvb_lm_head_argmax")
+    LaunchCounter.add(1)
+    return out

@@ -19,7 +19,8 @@ close.  So the prompt set is screened, once, here:
      eager on the device, with the fp32 gather-and-SDPA standing in for its attention package); the same margin is
      required of the reference's own logits;
   3. the first ``--keep`` prompts that pass both go into the fixture with the reference's tokens and margins; the
-     product engine is run once more on exactly that set, as the test will run it.
+     product engine is run once more on exactly that set, as the test will run it (its default configuration, in
+     which greedy steps go through the fused lm_head + argmax kernel; the screening runs materialise logits).
 
 Nothing is dropped for disagreeing: a prompt that passes both margin screens and still differs is kept and counted
 (``mismatches_after_screen``) - it would mean the implementations are more than a rounding apart.  The first 64
@@ -65,8 +66,10 @@ def test_engine_config() -> Config:
 
 
 def product_generate(engine: Engine, prompts):
-    """Tokens and per-step (largest, second largest) logits of every request, through ``Engine.generate``."""
+    """Tokens and per-step (largest, second largest) logits of every request, through ``Engine.generate``.
+    (The engine must materialise its logits for this: ``fused_greedy_head=False``.)"""
     ex = engine.executor
+    assert not ex.fused_head, "margins can only be recorded when the logits exist"
     order, tops = [], []
     launch, sampler = ex.launch, ex.sampler
 
@@ -120,7 +123,7 @@ def main():
     # ---- the big engine for screening -------------------------------------------------------------------
     big = Engine(Config(hf_config=qwen3_shape(), kv_cache_num_blocks=4 * 512 + 64, max_num_batched_seqs=512,
                         max_graph_batch_size=512, max_num_batched_tokens=16384, gpu_memory_utilization=0.6,
-                        use_cuda_graph=True, seed=0))
+                        use_cuda_graph=True, seed=0, fused_greedy_head=False))
     weights = reference_names({k: v.detach() for k, v in big.executor.model.state_dict().items()}, "qwen3",
                               big.config.hf_config)
 
@@ -199,8 +202,9 @@ def main():
     # ---- the kept set through the engine the test will build ------------------------------------------------
     del big
     torch.cuda.empty_cache()
-    small = Engine(test_engine_config())
-    final_tokens, final_top2 = product_generate(small, kept_prompts)
+    small = Engine(test_engine_config())                       # the default engine: fused lm_head + argmax, no logits
+    out = small.generate(kept_prompts, SamplingParams(max_tokens=STEPS, ignore_eos=True), use_tqdm=False)
+    final_tokens = [o["tokens"] for o in out]
     same = [a == b for a, b in zip(final_tokens, kept_ref_tokens)]
     print(f"kept set: {sum(same)}/{len(same)} identical to the reference over {STEPS} tokens", flush=True)
 
@@ -209,7 +213,7 @@ def main():
         args.out, prompt_lens=lens, prompts_flat=np.concatenate([np.asarray(p, np.int32) for p in kept_prompts]),
         ref_tokens=np.asarray(kept_ref_tokens, np.int32), ref_top2=np.asarray(kept_ref_top2, np.float32),
         ref_margin_ulps=margin_ulps(np.asarray(kept_ref_top2, np.float32)).astype(np.float32),
-        product_tokens=np.asarray(final_tokens, np.int32), product_top2=final_top2,
+        product_tokens=np.asarray(final_tokens, np.int32),
         reference_kind=np.asarray(ref_kind), seed=np.asarray(args.seed), min_ulps=np.asarray(args.min_ulps),
         candidates=np.asarray(n_cand), pass_product_margin=np.asarray(n_stage1), pass_both_margins=np.asarray(n_stage2),
         mismatches_after_screen=np.asarray(mismatches),

@@ -91,6 +91,19 @@ def test_greedy_tokens_match_oracle(cuda, family, shape, graphs):
     check_tokens(engine, family, prompts, params, cfg, got)
 
 
+def test_unfused_head_matches_oracle(cuda):
+    """``fused_greedy_head=False``: lm_head writes its logits and the sampler reads them, as the reference does."""
+    g = generator(15)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in randint(g, 5, 500, 8)]
+    params = [SamplingParams(max_tokens=24, ignore_eos=True) for _ in prompts]
+    cfg = Config(hf_config=small_qwen3(), kv_cache_num_blocks=40, max_num_batched_seqs=8, max_num_batched_tokens=2048,
+                 gpu_memory_utilization=0.3, seed=3, fused_greedy_head=False)
+    engine = Engine(cfg)
+    assert not engine.executor.fused_head
+    out = engine.generate(prompts, copy.deepcopy(params), use_tqdm=False)
+    check_tokens(engine, "qwen3", prompts, params, cfg, [o["tokens"] for o in out])
+
+
 def test_prefix_cache_and_preemption_match_oracle(cuda):
     """A tight pool (preemptions) with the prefix cache on: shared 512-token prefixes, same tokens as the oracle."""
     g = generator(6)
