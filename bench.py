@@ -318,7 +318,7 @@ def head_legs(dev, peaks) -> dict:
     out = {}
     hidden, vocab = 1024, 151936
     ws = [(torch.randn(vocab, hidden, device=dev) * 0.02).to(torch.bfloat16) for _ in range(2)]   # 2 x 311 MB > L2
-    for rows in (512, 64):
+    for rows in (512, 256, 128, 64):
         xs = [torch.randn(rows, hidden, device=dev).to(torch.bfloat16) for _ in range(2)]
         scratch = ops.lm_head_argmax_scratch(rows, dev)
         tok = torch.empty(rows, dtype=torch.int64, device=dev)

@@ -47,6 +47,7 @@ class Config:
     # True: a step whose requests all sample greedily (no top-k / top-p) runs lm_head and argmax as one kernel and
     # never materialises its logits.  False: lm_head, then the sampler, as the reference does.
     fused_greedy_head: bool = True
+    fused_head_max_rows: int = 256           # beyond this many rows cuBLAS + the greedy sampler are faster (measured)
 
     def __post_init__(self):
         if self.hf_config is None:

@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_greedy_kernel(const Sam
 constexpr int kKeptCap = 4096;       // kept (top-k) entries that the random path holds in shared memory
 constexpr int kRankCap = 1024;       // lists up to this length are ranked by pairwise comparison
 
-__global__ void __launch_bounds__(kSampleThreads, 3) sample_topk_gumbel_kernel(const SampleParams p) {
+__global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(const SampleParams p) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   const int parts = static_cast<int>(cluster.num_blocks()), part = static_cast<int>(cluster.block_rank());

@@ -69,7 +69,8 @@ class Executor:
         self.token_table = torch.zeros(0, dtype=torch.int64, device=self.device)   # last token per request slot
         self._out_ring = torch.zeros(self.RING, max(config.max_num_batched_seqs, 1), dtype=torch.int64).pin_memory()
         self.fused_head = bool(getattr(config, "fused_greedy_head", True))
-        self._head_scratch = ops.lm_head_argmax_scratch(max(config.max_num_batched_seqs, 16), self.device)
+        self.fused_head_max_rows = int(getattr(config, "fused_head_max_rows", 256))
+        self._head_scratch = ops.lm_head_argmax_scratch(max(self.fused_head_max_rows, 16), self.device)
         self.h2d_bytes = 0                   # bytes uploaded by the packing path (for the bench's e2e line)
         self.d2h_bytes = 0
         self.graph_runner = None
@@ -225,7 +226,7 @@ class Executor:
         argmax kernel; otherwise lm_head, then the sampler."""
         temperatures, top_k, top_p = self._build_sample_input(requests)
         rows = hidden_rows.shape[0]
-        if self.fused_head and top_k is None and top_p is None and rows * 8 + 8 <= self._head_scratch.numel():
+        if self.fused_head and top_k is None and top_p is None and rows <= self.fused_head_max_rows:
             return self.model.greedy_tokens(hidden_rows, self._head_scratch, scatter_table=scatter_table,
                                             scatter_index=scatter_index, status=self.status)
         logits = self.model.lm_head(hidden_rows)
