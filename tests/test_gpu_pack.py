@@ -120,3 +120,23 @@ def test_prefill_large_random_against_oracle(cuda):
 def test_warmup_requests_without_blocks_get_slot_minus_one(cuda):
     out = run_prefill(cuda, [64] * 10, [0] * 10, [0] * 10, [], np.zeros(640, np.int32), False)
     assert (out["slot_mapping"] == -1).all() and out["cu_seqlens_q"].tolist() == list(range(0, 641, 64))
+
+
+def test_executor_build_block_table_alone(cuda):
+    """``Executor._build_block_table`` (executor.py:156-163) on its own: ``[B, max blocks]`` int32, rows right-padded
+    with -1, packed on the device from the requests' block lists.  Driven through the executor's method on an object
+    that carries only what the method reads."""
+    from types import SimpleNamespace
+    from mini_vllm_b200.executor.executor import Executor, _Staging
+    blocks = [[5, 9, 2], [7], [], [1, 3, 8, 11, 4, 6, 0], [10, 12]]
+    reqs = [SimpleNamespace(tokens=[0] * (len(b) * BS), blocks=b) for b in blocks]
+    ex = object.__new__(Executor)
+    ex.block_size, ex.status, ex._step, ex._stages = BS, ops.new_status(cuda), 0, [_Staging(cuda) for _ in range(Executor.RING)]
+    table = Executor._build_block_table(ex, reqs)
+    torch.cuda.synchronize()
+    ops.check_status(ex.status)
+    want = np.full((len(blocks), 7), -1, np.int32)
+    for i, b in enumerate(blocks):
+        want[i, :len(b)] = b
+    assert table.dtype == torch.int32 and np.array_equal(table.cpu().numpy(), want)
+    assert np.array_equal(want, opack.build_block_table(blocks))
