@@ -129,11 +129,11 @@ def build_config(workload: str = "config5") -> Config:
                   max_num_batched_tokens=16384, gpu_memory_utilization=0.5, use_cuda_graph=True, seed=0)
 
 
-def build_engine(local_rank: int, workload: str = "config5", mixed_steps: bool = False):
+def build_engine(local_rank: int, workload: str = "config5", mixed_steps: bool = False, fused_head: bool = True):
     import dataclasses
     from mini_vllm_b200.engine.engine import Engine
     torch.cuda.set_device(local_rank)
-    return Engine(dataclasses.replace(build_config(workload), enable_mixed_steps=mixed_steps))
+    return Engine(dataclasses.replace(build_config(workload), enable_mixed_steps=mixed_steps, fused_greedy_head=fused_head))
 
 
 class ContextSpy:
@@ -645,6 +645,8 @@ def main():
     ap.add_argument("--kernel-legs", nargs="?", const="all", default=None, metavar="LEGS",
                     help="only the fixed single-kernel cases (one 2.3 GB pool), then exit; optionally a comma list out "
                          "of " + ",".join(LEGS) + " to keep a profiler capture small")
+    ap.add_argument("--no-fused-head", action="store_true",
+                    help="variant: lm_head and the sampler as two kernels on every step (Config.fused_greedy_head=False)")
     ap.add_argument("--mixed-steps", action="store_true",
                     help="variant: prompts join steps of running decodes (Config.enable_mixed_steps)")
     ap.add_argument("--config3-step", action="store_true",
@@ -703,7 +705,7 @@ def main():
     peaks, peak_kind = measured_peaks()
 
     mine = workload_requests(args.workload, world, rank)
-    engine = build_engine(local_rank, args.workload, mixed_steps=args.mixed_steps)
+    engine = build_engine(local_rank, args.workload, mixed_steps=args.mixed_steps, fused_head=not args.no_fused_head)
     dev = engine.executor.device
     # At N > 1 the job goes through the host dispatcher: rank 0 holds every request of the job (the shares of all
     # ranks), scatters them by token cost over a gloo group, and gets the completions back.
