@@ -544,6 +544,28 @@ def config4_engine_step() -> dict:
             "prefill_job_ms": round(times[1], 2)}
 
 
+def config2_parity() -> dict:
+    """First-32-token greedy identity on the real config-2 shape against the committed reference tokens
+    (tests/golden/config2_tokens.npz: the reference's own engine loop on a B200, prompts screened for a top-1/top-2
+    margin of more than one bf16 step at every step of the reference)."""
+    import numpy as np
+    from mini_vllm_b200.engine.engine import Engine
+    z = np.load(ROOT / "tests" / "golden" / "config2_tokens.npz")
+    cuts = np.concatenate([[0], np.cumsum(z["prompt_lens"])])
+    prompts = [z["prompts_flat"][a:b].tolist() for a, b in zip(cuts[:-1], cuts[1:])]
+    eng = Engine(build_config("config2"))
+    out = eng.generate(prompts, SamplingParams(max_tokens=32, ignore_eos=True), use_tqdm=False)
+    got = np.asarray([o["tokens"] for o in out], dtype=np.int32)
+    same = (got == z["ref_tokens"]).all(axis=1)
+    return {"prompts": len(prompts), "tokens_per_prompt": 32, "identical_prompts": int(same.sum()),
+            "identical_tokens": int((got == z["ref_tokens"]).sum()), "reference": str(z["reference_kind"]),
+            "min_reference_margin_bf16_steps": float(z["ref_margin_ulps"].min()),
+            "screen": {"candidates": int(z["candidates"]), "pass_product_margin": int(z["pass_product_margin"]),
+                       "pass_both_margins": int(z["pass_both_margins"]),
+                       "differ_after_screen": int(z["mismatches_after_screen"])},
+            "unscreened_identical_of_64": int(z["unscreened_identical"])}
+
+
 # ---- CPU leg: the oracle restatement of the reference path on the host cores ------------------------
 class CpuReference:
     """The oracle model (restatement of the reference's PyTorch path, pinned to the reference's own engine loop by
@@ -652,6 +674,9 @@ def main():
     ap.add_argument("--config3-step", action="store_true",
                     help="engine-level config 3: 16 prefix-cached prompts arriving among 240 decodes, as one mixed "
                          "step and as the reference's two steps")
+    ap.add_argument("--config2-parity", action="store_true",
+                    help="first-32-token greedy identity with the reference engine's committed tokens on the 28-layer "
+                         "config-2 model (64 screened prompts)")
     ap.add_argument("--config4-step", action="store_true",
                     help="engine-level config 4: a decode step of 128 sequences on Gemma3-1B shapes")
     ap.add_argument("--engine-steps", type=int, default=0,
@@ -666,6 +691,10 @@ def main():
             out.append(config3_engine_step(mixed))
             torch.cuda.empty_cache()
         print(json.dumps({"config3_engine_step": out}))
+        return
+    if args.config2_parity:
+        torch.cuda.set_device(0)
+        print(json.dumps({"config2_parity": config2_parity()}))
         return
     if args.config4_step:
         torch.cuda.set_device(0)

@@ -262,24 +262,37 @@ def generate_over_ranks(engine, prompts, sampling_params, group=None, src: int =
     the shares, every rank generates its share, ``src`` gathers the completions and returns them in submission
     order; the other ranks return ``None``.  ``group`` should be a gloo group: the payload is host objects.
     """
+    import numpy as np
     import torch.distributed as dist
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     shares = parts = None
     if rank == src:
         params = _as_list(sampling_params, len(prompts))
         parts = partition_by_tokens([request_cost(len(p), sp.max_tokens) for p, sp in zip(prompts, params)], world)
-        shares = [([prompts[i] for i in idx], [params[i] for i in idx]) for idx in parts]
+        # token ids travel as one int32 array per share (a pickled list of Python ints is five times the bytes)
+        shares = [(np.fromiter((t for i in idx for t in prompts[i]), np.int32),
+                   np.fromiter((len(prompts[i]) for i in idx), np.int64, len(idx)), [params[i] for i in idx])
+                  for idx in parts]
     mine = [None]
     dist.scatter_object_list(mine, shares, src=dist.get_global_rank(group, src) if group is not None else src,
                              group=group)
-    my_prompts, my_params = mine[0]
+    flat, lens, my_params = mine[0]
+    cuts = np.concatenate([[0], np.cumsum(lens)])
+    my_prompts = [flat[a:b].tolist() for a, b in zip(cuts[:-1], cuts[1:])]
     outs = engine.generate(my_prompts, my_params, use_tqdm=False) if my_prompts else []
+    packed = (np.fromiter((t for o in outs for t in o["tokens"]), np.int32),
+              np.fromiter((len(o["tokens"]) for o in outs), np.int64, len(outs)),
+              [{k: v for k, v in o.items() if k != "tokens"} for o in outs])
     gathered = [None] * world if rank == src else None
-    dist.gather_object(outs, gathered, dst=dist.get_global_rank(group, src) if group is not None else src,
+    dist.gather_object(packed, gathered, dst=dist.get_global_rank(group, src) if group is not None else src,
                        group=group)
     if rank != src:
         return None
-    return merge_outputs(parts, gathered, len(prompts))
+    per_part = []
+    for flat, lens, rest in gathered:
+        cuts = np.concatenate([[0], np.cumsum(lens)])
+        per_part.append([dict(r, tokens=flat[a:b].tolist()) for r, a, b in zip(rest, cuts[:-1], cuts[1:])])
+    return merge_outputs(parts, per_part, len(prompts))
 
 
 def visible_device_count() -> int:
