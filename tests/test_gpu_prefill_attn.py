@@ -125,3 +125,27 @@ def test_many_short_sequences_between_long_ones(cuda):
         run_dense(cuda, lens, 16, 8, 128, seed=20 + rep, packed_qkv=True)
     k_lens = lens[:24]
     run_paged(cuda, k_lens, k_lens, 16, 8, 128, seed=30)
+
+
+@pytest.mark.parametrize("boost", [6.0, 30.0])
+def test_logits_that_jump_between_key_tiles(cuda, boost):
+    """Keys whose logits are far larger in later tiles than in earlier ones (and the other way round): the running
+    softmax reference has to move by much more than its lazy threshold from one key tile to the next, in the middle
+    of a sequence, and the result must still be the oracle's."""
+    g = generator(71)
+    lens = [900, 400, 1300]
+    T = sum(lens)
+    q, k, v = randn_bf16(g, T, 16, 128), randn_bf16(g, T, 8, 128), randn_bf16(g, T, 8, 128)
+    k = k.float()
+    k[300:520] *= boost            # a loud stretch inside the first sequence (tiles 2-4), quiet again afterwards
+    k[900 + 256:900 + 400] *= boost
+    k[1300 + 1100:] *= boost       # the last tiles of the third sequence
+    k = k.to(torch.bfloat16)
+    cq = cu(lens)
+    want = oattn.prefill(q, k, v, cq, cq)
+    status = ops.new_status(cuda)
+    out = ops.prefill_attn(q.to(cuda), k.to(cuda), v.to(cuda), cq.to(cuda), cq.to(cuda), max(lens), 128 ** -0.5, -1,
+                           status=status)
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    assert_close_attn(out, want, f"logit jumps x{boost}")
