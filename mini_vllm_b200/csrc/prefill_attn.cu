@@ -12,12 +12,18 @@
 //                   paged pool are addressed through the block table (a tile never straddles a
 //                   block); zero-fills V rows past the end of the sequence (pool slots that were
 //                   never written may hold NaNs);
-//   MMA warp        one thread issues every tcgen05.mma: S_t = Q_t K^T (M=128, N=BN, fp32
-//                   accumulators in tensor memory) and O_t += P_t V with P read from tensor
-//                   memory (it overwrites S in place as packed bf16) and V consumed MN-major
-//                   straight from the TMA layout.  The two query tiles are interleaved
-//                   (S0, PV1, S1, PV0, ...) so the tensor pipe works on one tile while the other
-//                   tile's softmax runs;
+//   MMA warps       one issuing thread per query tile.  Per KV tile j thread t issues one burst:
+//                   O_t += P_t(j-1) V(j-1) with P read from tensor memory (it overwrites S in place
+//                   as packed bf16) and V consumed MN-major straight from the TMA layout, then
+//                   S_t(j) = Q_t K(j)^T (M=128, N=BN, fp32 accumulators in tensor memory), which
+//                   overwrites P_t(j-1).  A tcgen05.mma of this size costs its issuing thread about
+//                   as long as the tensor pipe needs to run it, and every wait or commit of that
+//                   thread adds to it, so one thread for both tiles is the bottleneck; two threads
+//                   left alone fall into step (both softmax groups then meet on the MUFU, both
+//                   bursts on the tensor pipe).  The bursts therefore strictly alternate (a token
+//                   passed through two barriers): one tile's products run under the other tile's
+//                   softmax.  The first 64 keys of P_t V are issued outside the turn, while the
+//                   softmax group is still exponentiating the other 64;
 //   softmax groups  one warpgroup per query tile, one thread per row: tcgen05.ld brings the row of
 //                   S into registers (no shuffles), running max / sum, exp2, P back to tensor
 //                   memory, O rescaled in tensor memory only when the running max moved by more
@@ -54,14 +60,15 @@ struct PrefillParams {
 
 // barrier slots
 // P is published in 64-key halves (slot B_PFULL + 2 * tile + half) so the PV product of the first
-// half starts while the second half is still being exponentiated.
+// half starts while the second half is still being exponentiated.  B_TURN + t: tile t's issuing thread
+// may issue its next burst.
 enum : int { B_QFULL = 0, B_KFULL = 2, B_VFULL = 4, B_KFREE = 6, B_VFREE = 8, B_SFULL = 10, B_PFULL = 12,
-             B_ODONE = 16, B_OFREE = 18, B_VFIXED = 20, B_QFREE = 22, B_ITEM_FULL = 23, B_ITEM_FREE = 25,
-             B_CLC = 27, B_COUNT = 28 };
+             B_TURN = 28, B_ODONE = 16, B_OFREE = 18, B_VFIXED = 20, B_QFREE = 22, B_ITEM_FULL = 23, B_ITEM_FREE = 25,
+             B_CLC = 27, B_COUNT = 30 };
 
 template <int D, int BN, int NQ>
 struct PrefillCfg {
-  static constexpr int THREADS = NQ * 128 + 64;
+  static constexpr int THREADS = NQ * 128 + 32 + NQ * 32;   // softmax groups, producer warp, one MMA warp per query tile
   static constexpr int Q_BYTES = 128 * D * 2;          // one query tile
   static constexpr int KV_BYTES = BN * D * 2;          // one K (or V) tile
   static constexpr int HALF_Q = 128 * 128;             // bytes of one 64-column half of a Q tile
@@ -69,7 +76,7 @@ struct PrefillCfg {
   // after the tiles: barriers, the tensor-memory address, the failure flag, two item slots and the
   // launch-control response
   static constexpr int CTRL_BYTES = 512;
-  static constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_FAIL = OFF_TMEM_SLOT + 4, OFF_ITEMS = 240, OFF_CLC = 272;
+  static constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_FAIL = OFF_TMEM_SLOT + 4, OFF_ITEMS = 256, OFF_CLC = 288;
   static constexpr int STAGE_BYTES = NQ * 4 * 4096;     // a 32-row x 128-byte output staging tile per softmax warp
   static constexpr int SMEM = NQ * Q_BYTES + 4 * KV_BYTES + 1024 /*align*/ + CTRL_BYTES + STAGE_BYTES;
   static constexpr int TMEM_COLS = NQ * (BN + D) <= 256 ? 256 : 512;   // power of two
@@ -164,11 +171,13 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       uint32_t count = 1u;
       if (i >= B_PFULL && i < B_PFULL + 4) count = 4u;          // one lane per softmax warp
       if (i >= B_OFREE && i < B_OFREE + 2) count = 4u;
-      if (i >= B_ITEM_FREE && i < B_ITEM_FREE + 2) count = 1u + NQ * 128u;
+      if ((i >= B_KFREE && i < B_KFREE + 4) || i == B_QFREE) count = NQ;   // every MMA thread releases every stage
+      if (i >= B_ITEM_FREE && i < B_ITEM_FREE + 2) count = NQ + NQ * 128u;
       mbar_init(&bars[i], count);
     }
     *fail_flag = 0;
     fence_mbar_init();
+    mbar_arrive(&bars[B_TURN + 0]);                           // the first burst is tile 0's
   }
   if (warp == NQ * 4 + 1) {                                   // the MMA warp owns the tensor memory
     tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -332,120 +341,103 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         if (v_issued >= back) mbar_wait(&bars[B_VFULL + ((v_issued - back) & 1)], ((v_issued - back) >> 1) & 1);
       }
     }
-  } else if (warp == NQ * 4 + 1) {
-    // ============================ MMA warp (one issuing thread) ======================================
-    // This thread shares its scheduler with two softmax warps that always have work, so every
-    // instruction between two tcgen05.mma costs tensor-pipe time: ranges are scalars, tile indices
-    // are compile-time constants and a wait is one try_wait unless the barrier is really not ready.
+  } else if (warp >= NQ * 4 + 1) {
+    // ============================ MMA warps: one issuing thread per query tile =========================
+    // Thread t issues, per KV tile j, one burst: O_t += P_t(j-1) V(j-1), then S_t(j) = Q_t K(j)^T.  The
+    // bursts of the two threads strictly alternate (B_TURN).  Both threads walk every KV tile of every
+    // item and release every ring stage, also in steps their tile sits out.
+    const int t = warp - (NQ * 4 + 1);
     if (lane == 0) {
       bool ok = true;
-      const uint64_t q_desc0 = umma_desc_sw128(q_s, 16, 1024);
+      const uint64_t q_desc = umma_desc_sw128(q_s + t * C::Q_BYTES, 16, 1024);
       const uint64_t k_desc0 = umma_desc_sw128(k_s, 16, 1024);
       const uint64_t v_desc0 = umma_desc_sw128(v_s, C::HALF_KV, 1024);
-      uint32_t g = 0;                                         // KV tiles consumed (ring position)
-      uint32_t n_pv[2] = {0, 0};                              // PV products issued per query tile (P parity)
-      uint32_t n_act[2] = {0, 0};                             // items in which the query tile had rows (Q / O parity)
+      const uint32_t s_tm = tmem + C::S_COL + t * BN, o_tm = tmem + C::O_COL + t * D;
+      uint32_t g = 0;                                         // KV tiles walked (ring position)
+      uint32_t n_pv = 0;                                      // PV products issued (P parity)
+      uint32_t n_act = 0;                                     // items in which this tile had rows (Q / O parity)
+      uint32_t n_burst = 0;                                   // bursts issued (turn parity)
       uint32_t fix_parity = 0;                                // bit st: parity of the next V fix-up on ring stage st
-      int jlo0 = 0, jhi0 = -1, jlo1 = 0, jhi1 = -1, j_lo = 0, j_partial = 0;
       auto ready = [&](int slot, uint32_t parity, int where) -> bool {
         return mbar_try_wait(&bars[slot], parity) ? true : wait(slot, parity, where);
       };
-      auto issue_s = [&](auto tt, int st) {                   // S_t = Q_t . K^T
-        constexpr int t = decltype(tt)::value;
-        const uint64_t qd = q_desc0 + ((t * C::Q_BYTES) >> 4), kd = k_desc0 + ((st * C::KV_BYTES) >> 4);
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t qo = ((ks >> 2) * C::HALF_Q + (ks & 3) * 32) >> 4, ko = ((ks >> 2) * C::HALF_KV + (ks & 3) * 32) >> 4;
-          umma_bf16_ss(tmem + C::S_COL + t * BN, qd + qo, kd + ko, IDESC_S, ks > 0);
-        }
-        umma_commit(&bars[B_SFULL + t]);
-      };
-      // O_t (+)= P_t . V for the KV tile at ring position gk (tile j of the sequence): V must have
-      // landed (and been fixed up if partial); the halves of P_t are consumed as the softmax group
-      // publishes them.  The first product of an item overwrites O_t, which the previous item's
-      // epilogue must have read out.
-      auto pv_step = [&](auto tt, uint32_t gk, int j, bool v_known) {
-        constexpr int t = decltype(tt)::value;
-        const int st = gk & 1;
-        const int jlo = t == 0 ? jlo0 : jlo1;
-        if (!v_known) {
-          ok = ready(B_VFULL + st, (gk >> 1) & 1, 400);
-          if (ok && j >= j_partial) ok = ready(B_VFIXED + st, (fix_parity >> st) & 1, 450);
-        }
-        const uint64_t vd = v_desc0 + ((st * C::KV_BYTES) >> 4);
-        uint32_t first = 1u;
-        if (j == jlo) {
-          first = 0u;
-          if (ok && n_act[t] > 0) ok = ready(B_OFREE + t, (n_act[t] - 1) & 1, 460);
-        }
-#pragma unroll
-        for (int h = 0; h < BN / 64; ++h) {
-          if (ok) ok = ready(B_PFULL + 2 * t + h, n_pv[t] & 1, 500);
-          if (!ok) return;
-          tc_fence_after();
-#pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            const int ks = h * 4 + k4;
-            umma_bf16_ts(tmem + C::O_COL + t * D, tmem + C::S_COL + t * BN + ks * 8, vd + ((ks * 2048) >> 4), IDESC_O,
-                         ks > 0 ? 1u : first);
-          }
-        }
-        if (j == (t == 0 ? jhi0 : jhi1)) umma_commit(&bars[B_ODONE + t]);   // the item's last product: the epilogue waits for it
-        ++n_pv[t];
-      };
-      using T0 = std::integral_constant<int, 0>;
-      using T1 = std::integral_constant<int, NQ - 1>;
       Item item;
       for (uint32_t n_item = 0; ok && next_item(n_item, item); ++n_item) {
-        jlo0 = item.jlo[0]; jhi0 = item.jhi[0];
-        jlo1 = item.jlo[NQ - 1]; jhi1 = item.jhi[NQ - 1];     // tile NQ-1 (== tile 0 when NQ == 1)
-        j_lo = item.j_lo;
-        j_partial = item.k_len / BN;                          // first KV tile with rows past the end
-        const int n_it = item.n_it;
-        const bool rows1 = item.rows[NQ - 1] > 0;
-        bool prev_a0 = false, prev_a1 = false;                // was tile 0 / tile NQ-1 active in the previous step
-        // With two tiles the loop takes one extra step for the last P_1 V, so that the tail runs the
-        // loop's own (warm) code.
-        for (int it = 0; it < n_it + (NQ > 1 ? 1 : 0) && ok; ++it, ++g) {
-          const int st = g & 1, j = j_lo + it;
+        int rows = item.rows[0], jlo = item.jlo[0], jhi = item.jhi[0];
+#pragma unroll
+        for (int u = 1; u < NQ; ++u)
+          if (t == u) { rows = item.rows[u]; jlo = item.jlo[u]; jhi = item.jhi[u]; }
+        if (rows <= 0) { jlo = 1; jhi = 0; }                  // this tile sits the item out (it still walks the ring)
+        const int j_partial = item.k_len / BN;                // first KV tile with rows past the end
+        const int n_it = item.n_it, j_lo = item.j_lo;
+        // step `it`: PV of KV tile j - 1, then S of tile j; one extra step for the last PV
+        for (int it = 0; it <= n_it && ok; ++it) {
+          const int j = j_lo + it;
           const bool body = it < n_it;
-          bool a0 = false;
-          if (body) {
-            ok = ready(B_KFULL + st, (g >> 1) & 1, 600);
-            if (!ok) break;
-            tc_fence_after();
-            a0 = j >= jlo0 && j <= jhi0;
-            // interleave the tiles: S0(j), PV1(j-1), S1(j), PV0(j)
-            if (a0) {
-              if (j == jlo0) ok = ready(B_QFULL + 0, n_act[0] & 1, 610);
-              if (ok) issue_s(T0{}, st);
+          const bool act_s = body && j >= jlo && j <= jhi;
+          const bool act_pv = it >= 1 && j - 1 >= jlo && j - 1 <= jhi;
+          const int st = g & 1, stp = (g - 1) & 1;            // ring stages of tile j and of tile j - 1
+          // everything the burst needs, then the turn
+          if (body) ok = ready(B_KFULL + st, (g >> 1) & 1, 600);
+          if (ok && act_s && j == jlo) ok = ready(B_QFULL + t, n_act & 1, 610);
+          if (ok && it >= 1) {
+            ok = ready(B_VFULL + stp, ((g - 1) >> 1) & 1, 400);
+            if (ok && j - 1 >= j_partial) ok = ready(B_VFIXED + stp, (fix_parity >> stp) & 1, 450);
+          }
+          uint32_t first = 1u;
+          if (ok && act_pv) {
+            if (j - 1 == jlo) {
+              first = 0u;                                     // an item's first product overwrites O_t: the previous epilogue has read it
+              if (n_act > 0) ok = ready(B_OFREE + t, (n_act - 1) & 1, 460);
+            }
+            if (ok) ok = ready(B_PFULL + 2 * t, n_pv & 1, 500);
+          }
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t vd = v_desc0 + ((stp * C::KV_BYTES) >> 4);
+          if (act_pv) {                                       // O_t (+)= P_t . V, first 64 keys: under the softmax of the other 64
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_bf16_ts(o_tm, s_tm + ks * 8, vd + ((ks * 2048) >> 4), IDESC_O, ks > 0 ? 1u : first);
+            if constexpr (BN > 64) {
+              ok = ready(B_PFULL + 2 * t + 1, n_pv & 1, 501);
             }
           }
           if constexpr (NQ > 1) {
-            if (it >= 1 && ok) {
-              if (prev_a1) pv_step(T1{}, g - 1, j - 1, prev_a0);   // tile 0's PV already waited for that V tile
-              if (ok) umma_commit(&bars[B_VFREE + ((g - 1) & 1)]);
-            }
-            if (!body) break;                                 // (leaves g on the next ring position)
-            const bool a1 = rows1 && j >= jlo1 && j <= jhi1;
-            if (ok && a1) {
-              if (j == jlo1) ok = ready(B_QFULL + NQ - 1, n_act[NQ - 1] & 1, 611);
-              if (ok) issue_s(T1{}, st);
-            }
-            prev_a1 = a1;
+            if (ok) ok = ready(B_TURN + t, n_burst & 1, 620);
           }
-          if (ok) {
+          if (!ok) break;
+          tc_fence_after();
+          if (act_pv) {
+            if constexpr (BN > 64) {
+#pragma unroll
+              for (int ks = 4; ks < BN / 16; ++ks)
+                umma_bf16_ts(o_tm, s_tm + ks * 8, vd + ((ks * 2048) >> 4), IDESC_O, 1u);
+            }
+            if (j - 1 == jhi) umma_commit(&bars[B_ODONE + t]);  // the item's last product: the epilogue waits for it
+            ++n_pv;
+          }
+          if (act_s) {                                        // S_t = Q_t . K^T
+            const uint64_t kd = k_desc0 + ((st * C::KV_BYTES) >> 4);
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+              const uint32_t qo = ((ks >> 2) * C::HALF_Q + (ks & 3) * 32) >> 4, ko = ((ks >> 2) * C::HALF_KV + (ks & 3) * 32) >> 4;
+              umma_bf16_ss(s_tm, q_desc + qo, kd + ko, IDESC_S, ks > 0);
+            }
+            umma_commit(&bars[B_SFULL + t]);
+          }
+          if constexpr (NQ > 1) mbar_arrive(&bars[B_TURN + (t ^ 1)]);
+          if (it >= 1) umma_commit(&bars[B_VFREE + stp]);
+          if (body) {
             umma_commit(&bars[B_KFREE + st]);
             if (it == n_it - 1) umma_commit(&bars[B_QFREE]);  // the item's last S product has been issued
           }
-          if (ok && a0) pv_step(T0{}, g, j, false);
-          if (NQ == 1 && ok) umma_commit(&bars[B_VFREE + st]);
-          prev_a0 = a0;
+          ++n_burst;
+          if (body) ++g;
         }
         // a partial tile is an item's last one: its fix-up, on the ring stage just left, has been consumed
         if (item.j_hi >= j_partial) fix_parity ^= 1u << ((g - 1) & 1);
-        ++n_act[0];
-        if (NQ > 1 && rows1) ++n_act[NQ - 1];
+        if (rows > 0) ++n_act;
       }
     }
     __syncwarp();
