@@ -236,7 +236,7 @@ def decode_roofline(engine, contexts, peaks):
             "note": "algorithmic K+V bytes of recorded decode steps, 28 layer launches replayed from a CUDA graph; peak = STREAM copy"}
 
 
-LEGS = ("attn3", "prefill", "attn4", "sampler", "rope", "pack", "head")
+LEGS = ("attn3", "prefill", "attn4", "sampler", "rope", "pack", "head", "glue")
 
 
 def graph_time_ms(sweep, launches_per_sweep: int, reps: int = 5) -> float:
@@ -284,6 +284,28 @@ def rope_and_pack_legs(dev, peaks, legs) -> dict:
                 out[f"{kern}_{name}"] = {"GB/s": round(byts / ms / 1e6, 1), "us": round(ms * 1e3, 2), "bytes": byts,
                                          "frac_of_measured_hbm": round(byts / ms / 1e6 / peaks["hbm_gbs"], 4)}
             del qkvs, pools, views
+    if "glue" in legs:
+        # the decoder glue between the GEMMs on config 3's prefill rows (Qwen3-0.6B: hidden 1024, intermediate 3072)
+        hidden, inter = 1024, 3072
+        for name, tokens in (("prefill12784", sum(q_lens)), ("decode512", 512)):
+            nbuf = max(2, min(8, int(400e6 / (tokens * inter * 6))))
+            gus = [torch.randn(tokens, 2 * inter, device=dev).to(torch.bfloat16) for _ in range(nbuf)]
+            outs = [torch.empty(tokens, inter, device=dev, dtype=torch.bfloat16) for _ in range(nbuf)]
+            byts = tokens * inter * 2 * 3
+            ms = graph_time_ms(lambda: [ops.act_mul(gu, inter, False, out=o) for gu, o in zip(gus, outs)], nbuf)
+            out[f"act_mul_{name}"] = {"GB/s": round(byts / ms / 1e6, 1), "us": round(ms * 1e3, 2), "bytes": byts,
+                                      "frac_of_measured_hbm": round(byts / ms / 1e6 / peaks["hbm_gbs"], 4)}
+            del gus, outs
+            nbuf = 8
+            xs = [torch.randn(tokens, hidden, device=dev).to(torch.bfloat16) for _ in range(nbuf)]
+            ys = [torch.randn(tokens, hidden, device=dev).to(torch.bfloat16) for _ in range(nbuf)]
+            os_ = [torch.empty(tokens, hidden, device=dev, dtype=torch.bfloat16) for _ in range(nbuf)]
+            w = torch.ones(hidden, device=dev, dtype=torch.bfloat16)
+            byts = tokens * hidden * 2 * 4                     # x and y read, x and the normed row written
+            ms = graph_time_ms(lambda: [ops.add_rmsnorm(x, y, w, 1e-6, False, out=o) for x, y, o in zip(xs, ys, os_)], nbuf)
+            out[f"add_rmsnorm_{name}"] = {"GB/s": round(byts / ms / 1e6, 1), "us": round(ms * 1e3, 2), "bytes": byts,
+                                          "frac_of_measured_hbm": round(byts / ms / 1e6 / peaks["hbm_gbs"], 4)}
+            del xs, ys, os_
     if "pack" in legs:
         # prefill packing of config 3's 16 prompts (12 784 new tokens, cached prefixes) and decode packing of 512 rows
         seq_len = np.asarray(case.prefill_lens, np.int32)

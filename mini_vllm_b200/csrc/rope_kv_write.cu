@@ -11,6 +11,8 @@
 #include "host_util.cuh"
 #include "mini_vllm_b200.h"
 
+#include <type_traits>
+
 namespace mvb {
 
 struct RopeParams {
@@ -82,20 +84,33 @@ struct NormRopeParams {
   int unit_offset;
 };
 
-template <int ITEMS, bool NORM>
+// PPH fixes the chunk pairs per head at compile time (8: head_dim 128, 16: head_dim 256; 0: read it from the
+// parameters), which turns the task -> (head, chunk) divisions of every group into shifts.
+template <int ITEMS, bool NORM, int PPH>
 __global__ void __launch_bounds__(256, 3) rope_kv_kernel(const NormRopeParams np) {
   const RopeParams& p = np.r;
-  const int pph = p.d / 16;                                  // chunk pairs per head
+  const int pph = PPH ? PPH : p.d / 16;                      // chunk pairs per head
+  const int d = PPH ? PPH * 16 : p.d;
   const int rope_tasks = (p.hq + p.hkv) * pph;               // per token
-  const int tasks = rope_tasks + p.hkv * p.d / 8;
+  const int tasks = rope_tasks + p.hkv * d / 8;
   const int groups = (tasks + 31) >> 5;
   const int warps_per_token = (groups + ITEMS - 1) / ITEMS;
-  const int64_t gwarp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  const int64_t t64 = gwarp / warps_per_token;
+  int64_t t64;
+  int warp_in_token;
+  if (gridDim.x <= 0x0fffffffu) {                            // the usual case: a 32-bit division
+    const uint32_t gwarp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t q = gwarp / static_cast<uint32_t>(warps_per_token);
+    t64 = q;
+    warp_in_token = static_cast<int>(gwarp - q * static_cast<uint32_t>(warps_per_token));
+  } else {
+    const int64_t gwarp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    t64 = gwarp / warps_per_token;
+    warp_in_token = static_cast<int>(gwarp - t64 * warps_per_token);
+  }
   if (t64 >= p.num_tokens) return;                           // warp-uniform
   const int t = static_cast<int>(t64);
-  const int task0 = static_cast<int>(gwarp - t64 * warps_per_token) * (ITEMS * 32) + lane;
+  const int task0 = warp_in_token * (ITEMS * 32) + lane;
   const bool rotate = p.cos_sin != nullptr;
 
   // ---- every load of this lane goes out before anything is used ------------------------------------------
@@ -108,9 +123,9 @@ __global__ void __launch_bounds__(256, 3) rope_kv_kernel(const NormRopeParams np
     lo[j] = make_uint4(0, 0, 0, 0); hi[j] = make_uint4(0, 0, 0, 0);
     if (task < rope_tasks) {
       const int head = task / pph, c = task - head * pph;
-      const __nv_bfloat16* row = head < p.hq ? p.q + t * p.q_stride + head * p.d : p.k + t * p.k_stride + (head - p.hq) * p.d;
+      const __nv_bfloat16* row = head < p.hq ? p.q + t * p.q_stride + head * d : p.k + t * p.k_stride + (head - p.hq) * d;
       lo[j] = *reinterpret_cast<const uint4*>(row + c * 8);
-      hi[j] = *reinterpret_cast<const uint4*>(row + p.d / 2 + c * 8);
+      hi[j] = *reinterpret_cast<const uint4*>(row + d / 2 + c * 8);
     } else if (task < tasks) {
       lo[j] = *reinterpret_cast<const uint4*>(p.v + t * p.v_stride + (task - rope_tasks) * 8);
     }
@@ -124,11 +139,11 @@ __global__ void __launch_bounds__(256, 3) rope_kv_kernel(const NormRopeParams np
   const bool same_chunk = (32 % pph) == 0;                   // the lane's chunk index does not depend on the group
   float cs[8], sn[8];
   auto load_table = [&](int c) {
-    const float* tab = p.cos_sin + pos * p.d;
+    const float* tab = p.cos_sin + pos * d;
     *reinterpret_cast<float4*>(cs) = *reinterpret_cast<const float4*>(tab + c * 8);
     *reinterpret_cast<float4*>(cs + 4) = *reinterpret_cast<const float4*>(tab + c * 8 + 4);
-    *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(tab + p.d / 2 + c * 8);
-    *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(tab + p.d / 2 + c * 8 + 4);
+    *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(tab + d / 2 + c * 8);
+    *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(tab + d / 2 + c * 8 + 4);
   };
   if (rotate && pos_ok && same_chunk && task0 < rope_tasks) load_table(task0 % pph);
 
@@ -154,10 +169,10 @@ __global__ void __launch_bounds__(256, 3) rope_kv_kernel(const NormRopeParams np
       // every lane of the warp takes part; a head's lanes form an aligned group of pph
       for (int off = 1; off < pph; off <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
       if (is_rope && (is_q || slot >= 0 || p.k_in_place)) {
-        const float rstd = rsqrtf(ss / static_cast<float>(p.d) + np.eps);
+        const float rstd = rsqrtf(ss / static_cast<float>(d) + np.eps);
         const __nv_bfloat16* w = is_q ? np.q_weight : np.k_weight;
         const uint4 wl = *reinterpret_cast<const uint4*>(w + c * 8);
-        const uint4 wh = *reinterpret_cast<const uint4*>(w + p.d / 2 + c * 8);
+        const uint4 wh = *reinterpret_cast<const uint4*>(w + d / 2 + c * 8);
         uint32_t* a = reinterpret_cast<uint32_t*>(&lo[j]);
         uint32_t* b = reinterpret_cast<uint32_t*>(&hi[j]);
         const uint32_t* wa = reinterpret_cast<const uint32_t*>(&wl);
@@ -173,7 +188,7 @@ __global__ void __launch_bounds__(256, 3) rope_kv_kernel(const NormRopeParams np
     if (task >= tasks) continue;
     if (!is_rope) {                                          // ---- V: plain copy to the cache slot
       if (slot >= 0)
-        *reinterpret_cast<uint4*>(p.v_cache + slot * (static_cast<int64_t>(p.hkv) * p.d) + (task - rope_tasks) * 8) = lo[j];
+        *reinterpret_cast<uint4*>(p.v_cache + slot * (static_cast<int64_t>(p.hkv) * d) + (task - rope_tasks) * 8) = lo[j];
       continue;
     }
     if (!is_q && slot < 0 && !p.k_in_place) continue;        // nothing to produce for this k chunk
@@ -182,15 +197,15 @@ __global__ void __launch_bounds__(256, 3) rope_kv_kernel(const NormRopeParams np
       if (!same_chunk) load_table(c);
       rotate8<!NORM>(lo[j], hi[j], cs, sn);
     }
-    __nv_bfloat16* row = is_q ? p.q + t * p.q_stride + head * p.d : p.k + t * p.k_stride + (head - p.hq) * p.d;
+    __nv_bfloat16* row = is_q ? p.q + t * p.q_stride + head * d : p.k + t * p.k_stride + (head - p.hq) * d;
     if ((is_q || p.k_in_place) && (rotate || NORM)) {
       *reinterpret_cast<uint4*>(row + c * 8) = lo[j];
-      *reinterpret_cast<uint4*>(row + p.d / 2 + c * 8) = hi[j];
+      *reinterpret_cast<uint4*>(row + d / 2 + c * 8) = hi[j];
     }
     if (!is_q && slot >= 0) {
-      __nv_bfloat16* dst = p.k_cache + slot * (static_cast<int64_t>(p.hkv) * p.d) + (head - p.hq) * p.d;
+      __nv_bfloat16* dst = p.k_cache + slot * (static_cast<int64_t>(p.hkv) * d) + (head - p.hq) * d;
       *reinterpret_cast<uint4*>(dst + c * 8) = lo[j];
-      *reinterpret_cast<uint4*>(dst + p.d / 2 + c * 8) = hi[j];
+      *reinterpret_cast<uint4*>(dst + d / 2 + c * 8) = hi[j];
     }
   }
 }
@@ -209,9 +224,15 @@ static int launch_rope(const NormRopeParams& np, cudaStream_t stream) {
   const int64_t blocks = (warps * 32 + 255) / 256;
   if (blocks > 0x7fffffffLL) return kInvalidArgument;
   const unsigned grid = static_cast<unsigned>(blocks);
-  if (items == 5) rope_kv_kernel<5, NORM><<<grid, 256, 0, stream>>>(np);
-  else if (items == 2) rope_kv_kernel<2, NORM><<<grid, 256, 0, stream>>>(np);
-  else rope_kv_kernel<1, NORM><<<grid, 256, 0, stream>>>(np);
+  auto launch = [&](auto pph_tag) {
+    constexpr int PPH = decltype(pph_tag)::value;
+    if (items == 5) rope_kv_kernel<5, NORM, PPH><<<grid, 256, 0, stream>>>(np);
+    else if (items == 2) rope_kv_kernel<2, NORM, PPH><<<grid, 256, 0, stream>>>(np);
+    else rope_kv_kernel<1, NORM, PPH><<<grid, 256, 0, stream>>>(np);
+  };
+  if (p.d == 128) launch(std::integral_constant<int, 8>{});
+  else if (p.d == 256) launch(std::integral_constant<int, 16>{});
+  else launch(std::integral_constant<int, 0>{});
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
