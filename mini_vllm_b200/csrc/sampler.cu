@@ -409,12 +409,55 @@ __global__ void __launch_bounds__(kSampleThreads, 2) sample_topk_gumbel_kernel(c
         const uint32_t slot = atomicAdd(&n_kept_s, 1u);
         if (slot < kKeptCap) { kept_col[slot] = c; kept_bits[slot] = bits; }
       };
-      for_each_word_slice(row, p.vocab, vec_ok, part, parts, [&](int c, uint32_t w) {
+      // Only a thread whose own sub-maxima reach the cut has such entries among its words: about k of the
+      // 2 * kSampleThreads sub-maxima do.  Those threads put their index on a list and the whole CTA then reads
+      // the listed threads' words again (from L2), a handful of loads per thread in one round trip, instead of
+      // every thread walking its own forty words four at a time.
+      auto scan = [&](int c, uint32_t w) {
         const uint32_t ge = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w), t2);
         if (ge == 0u) return;
         if (ge & 0xffffu) push(c, static_cast<uint16_t>(w & 0xffffu));
         if (ge >> 16) push(c + 1, static_cast<uint16_t>(w >> 16));
-      });
+      };
+      const bool mine = __hge2_mask(m2, t2) != 0u;
+      if (vec_ok) {
+        uint16_t* qlist = reinterpret_cast<uint16_t*>(hist_w);  // (the per-warp histograms are not in use here)
+        if (threadIdx.x == 0) sel_s[1] = 0u;
+        __syncthreads();
+        if (mine) qlist[atomicAdd(&sel_s[1], 1u)] = static_cast<uint16_t>(threadIdx.x);
+        __syncthreads();
+        const int n_q = static_cast<int>(sel_s[1]);
+        const int nvec = p.vocab / 8;
+        const int v0 = static_cast<int>(static_cast<int64_t>(nvec) * part / parts);
+        const int v1 = static_cast<int>(static_cast<int64_t>(nvec) * (part + 1) / parts);
+        const int per = (v1 - v0 + kSampleThreads - 1) / kSampleThreads;      // words of one thread
+        const int items = n_q * per;
+        for (int it = threadIdx.x; it < items; it += 4 * kSampleThreads) {
+          uint4 w[4];
+          int v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int item = it + u * kSampleThreads;
+            v[u] = v1;
+            if (item < items) {
+              const int qi = item / per, i = item - qi * per;
+              v[u] = v0 + static_cast<int>(qlist[qi]) + i * kSampleThreads;
+            }
+            if (v[u] < v1) w[u] = *reinterpret_cast<const uint4*>(row + v[u] * 8);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (v[u] < v1) { scan(v[u] * 8, w[u].x); scan(v[u] * 8 + 2, w[u].y); scan(v[u] * 8 + 4, w[u].z); scan(v[u] * 8 + 6, w[u].w); }
+        }
+        if (mine && part == parts - 1) {                       // the columns past the last whole 16-byte word
+          for (int c = nvec * 8 + 2 * threadIdx.x; c < p.vocab; c += 2 * kSampleThreads) {
+            const uint32_t lo = row[c], hi = c + 1 < p.vocab ? row[c + 1] : 0xff80u;
+            scan(c, lo | (hi << 16));
+          }
+        }
+      } else if (mine) {
+        for_each_word_slice(row, p.vocab, vec_ok, part, parts, scan);
+      }
     }
     __syncthreads();
     // 4. ... and from there into the first CTA's list, one reservation per CTA
