@@ -78,6 +78,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   return false;
 }
 
+// The slow side of a role's bounded wait, out of line on purpose: the prefill kernel has thirty waits, and inlined
+// at each of them this loop was most of the code its roles fetch (6 % faster with it here; the fused head, with
+// six waits, measured 2 % slower and keeps its own inline).  Gives up when another role has failed (fail_flag)
+// or after 64 x 2^14 polls, which it reports.
+static __device__ __noinline__ bool mbar_wait_or_fail(uint64_t* bar, uint32_t parity, volatile uint32_t* fail_flag,
+                                                      int* dev_status, int where) {
+  for (int spin = 0; spin < 64; ++spin) {
+    if (mbar_wait(bar, parity, 1u << 14)) return true;
+    if (*fail_flag) return false;
+  }
+  report(dev_status, kDevWaitTimeout, where);
+  *fail_flag = 1;
+  return false;
+}
+
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

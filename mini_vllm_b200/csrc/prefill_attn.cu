@@ -190,13 +190,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 
   // Bounded wait that also gives up when another role has failed.
   auto wait = [&](int slot, uint32_t parity, int where) -> bool {
-    for (int spin = 0; spin < 64; ++spin) {
-      if (mbar_wait(&bars[slot], parity, 1u << 14)) return true;
-      if (*fail_flag) return false;
-    }
-    report(p.dev_status, kDevWaitTimeout, where);
-    *fail_flag = 1;
-    return false;
+    if (mbar_try_wait(&bars[slot], parity)) return true;
+    return mbar_wait_or_fail(&bars[slot], parity, fail_flag, p.dev_status, where);
   };
   // The consumer side of the item ring: false at the end of the work (or on failure).
   auto next_item = [&](uint32_t n, Item& item) -> bool {
