@@ -431,12 +431,17 @@ def attention_legs_qwen3(dev, peaks, nl, legs):
     qp = torch.randn(sum(q_lens), hq, d, device=dev, dtype=torch.bfloat16)
     btp = table_tensor(case.prefill_blocks).to(dev)
     cq, ck = cu(q_lens), cu(case.prefill_lens)
-    ms = event_time_ms(lambda i: ops.prefill_attn(qp, pools[i % nl][0], pools[i % nl][1], cq, ck, max(q_lens), d ** -0.5,
-                                                  -1, block_table=btp), 10)
+    # the launch's work list, built on the host from the lengths as the executor does while packing the step
+    rows = ops.prefill_item_rows(hq, hkv, d)
+    work = lambda ql, kl: torch.from_numpy(ops.build_prefill_items(ql, kl, rows)).to(dev)
+    items = work(q_lens, case.prefill_lens)
     fl = prefill_flops(QWEN3_0P6B, case.prefill_lens, case.prefill_cached)
-    tf = fl / ms / 1e9
-    out["prefill_attn_config3"] = {"TFLOP/s": round(tf, 1), "us": round(ms * 1e3, 1), "flops": fl,
-                                   "frac_of_measured_bf16": round(tf / peaks["bf16_tflops"], 4)}
+    for name, it in (("prefill_attn_config3", items), ("prefill_attn_config3_no_list", None)):
+        ms = event_time_ms(lambda i: ops.prefill_attn(qp, pools[i % nl][0], pools[i % nl][1], cq, ck, max(q_lens), d ** -0.5,
+                                                      -1, block_table=btp, items=it), 10)
+        tf = fl / ms / 1e9
+        out[name] = {"TFLOP/s": round(tf, 1), "us": round(ms * 1e3, 1), "flops": fl,
+                     "frac_of_measured_bf16": round(tf / peaks["bf16_tflops"], 4)}
     del pools
     # the same kernel on long and on short prompts (dense K/V): 4 x 8192 and 32 x 1024 tokens
     for name, (nseq, slen) in (("prefill_attn_4x8192", (4, 8192)), ("prefill_attn_32x1024", (32, 1024))):
@@ -445,10 +450,11 @@ def attention_legs_qwen3(dev, peaks, nl, legs):
         kd = torch.randn(nseq * slen, hkv, d, device=dev, dtype=torch.bfloat16)
         vd = torch.randn(nseq * slen, hkv, d, device=dev, dtype=torch.bfloat16)
         cd = cu(lens_p)
-        ms = event_time_ms(lambda i: ops.prefill_attn(qd, kd, vd, cd, cd, slen, d ** -0.5, -1), 10)
         fl = prefill_flops(QWEN3_0P6B, lens_p, [0] * nseq)
-        out[name] = {"TFLOP/s": round(fl / ms / 1e9, 1), "us": round(ms * 1e3, 1), "flops": fl,
-                     "frac_of_measured_bf16": round(fl / ms / 1e9 / peaks["bf16_tflops"], 4)}
+        for key, it in ((name, work(lens_p, lens_p)), (name + "_no_list", None)):
+            ms = event_time_ms(lambda i: ops.prefill_attn(qd, kd, vd, cd, cd, slen, d ** -0.5, -1, items=it), 10)
+            out[key] = {"TFLOP/s": round(fl / ms / 1e9, 1), "us": round(ms * 1e3, 1), "flops": fl,
+                        "frac_of_measured_bf16": round(fl / ms / 1e9 / peaks["bf16_tflops"], 4)}
         del qd, kd, vd
     return out
 

@@ -31,6 +31,9 @@ SIGNATURES = {
                                      i64, vp, vp]),
     "mvb_prefill_attn": (i32, [vp, i64, vp, i64, vp, i64, i64, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, f32,
                                i32, vp, i64, vp, vp]),
+    "mvb_prefill_item_rows": (i32, [i32, i32, i32]),
+    "mvb_prefill_attn_items": (i32, [vp, i64, vp, i64, vp, i64, i64, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32,
+                                     f32, i32, vp, i64, vp, i32, vp, vp]),
     "mvb_act_mul": (i32, [vp, i64, vp, i64, i32, i32, i32, vp]),
     "mvb_add_rmsnorm": (i32, [vp, vp, i64, vp, vp, vp, i32, i32, f32, i32, vp]),
     "mvb_add_rmsnorm_last_tokens": (i32, [vp, vp, i64, vp, vp, vp, vp, i32, i32, f32, i32, vp]),

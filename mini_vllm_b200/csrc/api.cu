@@ -2,7 +2,7 @@
 #include "common.cuh"
 #include "mini_vllm_b200.h"
 
-extern "C" int mvb_abi_version(void) { return 5; }
+extern "C" int mvb_abi_version(void) { return 6; }
 
 extern "C" const char* mvb_status_string(int status) {
   switch (status) {

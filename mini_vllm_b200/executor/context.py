@@ -33,6 +33,11 @@ class Context:
     # extension (mixed step): the last num_decode sequences of a prefill-shaped step hold one query token each
     # and are attended by the decode kernel; cache_seqlens then holds THEIR lengths
     num_decode: int = 0
+    # extension: the prefill launch's work as a list, int32 [n, 2] of (sequence, query block) with the blocks that
+    # see the most keys first, built on the host while packing (ops.build_prefill_items) for query blocks of
+    # prefill_item_rows rows; the attention layer hands it to the kernel when its head layout uses that block size
+    prefill_items: Optional[torch.Tensor] = field(default=None, repr=False, compare=False)
+    prefill_item_rows: int = 0
 
     # filled by the attention layer on first use within this forward pass
     decode_plans: dict = field(default_factory=dict, repr=False, compare=False)

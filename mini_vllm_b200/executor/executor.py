@@ -71,6 +71,11 @@ class Executor:
         self.fused_head = bool(getattr(config, "fused_greedy_head", True))
         self.fused_head_max_rows = int(getattr(config, "fused_head_max_rows", 256))
         self._head_scratch = ops.lm_head_argmax_scratch(max(self.fused_head_max_rows, 16), self.device)
+        hf = config.hf_config
+        try:                                   # query-block size of the prefill kernel's work items for this model
+            self.item_rows = ops.prefill_item_rows(hf.num_attention_heads, hf.num_key_value_heads, hf.head_dim)
+        except Exception:
+            self.item_rows = 0                 # (a head layout the kernel does not take: no list, the plain grid)
         self.h2d_bytes = 0                   # bytes uploaded by the packing path (for the bench's e2e line)
         self.d2h_bytes = 0
         self.graph_runner = None
@@ -130,15 +135,25 @@ class Executor:
         new_tokens = np.fromiter(
             itertools.chain.from_iterable(r.tokens[r.num_cached_tokens:] if r.num_cached_tokens else r.tokens
                                           for r in requests), np.int32, t)
-        meta = self._stage.upload([seq_len, cached, blk_off, blocks, new_tokens])
+        items = self._prefill_items(q_len, seq_len)
+        meta = self._stage.upload([seq_len, cached, blk_off, blocks, new_tokens, items.reshape(-1)])
         self.h2d_bytes += meta.numel() * 4
         width = max(int(nblk.max()), 1)
         out = ops.pack_prefill(meta, b, t, int(blk_off[-1]), width, self.block_size, bool(cached.any()), self.status)
         ctx = Context(prefill=True, positions=out["positions"], cu_seqlens_q=out["cu_seqlens_q"],
                       cu_seqlens_k=out["cu_seqlens_k"], slot_mapping=out["slot_mapping"],
                       max_seqlen_q=int(q_len.max()), max_seqlen_k=int(seq_len.max()),
-                      block_table=out["block_table"], status=self.status)
+                      block_table=out["block_table"], status=self.status,
+                      prefill_items=meta[meta.numel() - items.size:].view(-1, 2) if items.size else None,
+                      prefill_item_rows=self.item_rows)
         return out["input_ids"], ctx
+
+    def _prefill_items(self, q_len: np.ndarray, seq_len: np.ndarray) -> np.ndarray:
+        """The prefill kernel's work list for this step (ops.build_prefill_items): the host has the lengths in
+        hand here, so the launch gets exactly its real (sequence, query block) items, longest first."""
+        if not self.item_rows:
+            return np.zeros((0, 2), np.int32)
+        return ops.build_prefill_items(q_len, seq_len, self.item_rows)
 
     def _build_mixed_input(self, requests: list[Request], num_decode: int, slots: np.ndarray | None = None):
         """One ragged step: the first requests prefill, the last ``num_decode`` decode.  A decoding request
@@ -153,15 +168,20 @@ class Executor:
         new_tokens = np.fromiter(
             itertools.chain(itertools.chain.from_iterable(r.tokens[r.num_cached_tokens:] for r in requests[:bp]),
                             (r.tokens[-1] for r in requests[bp:])), np.int32, t)
-        meta = self._stage.upload([seq_len, cached, blk_off, blocks, new_tokens] + ([slots] if slots is not None else []))
+        items = self._prefill_items(q_len[:bp], seq_len[:bp])           # the prompts' part of the step
+        meta = self._stage.upload([seq_len, cached, blk_off, blocks, new_tokens, items.reshape(-1)]
+                                  + ([slots] if slots is not None else []))
         self.h2d_bytes += meta.numel() * 4
         width = max(int(nblk.max()), 1)
         out = ops.pack_prefill(meta, b, t, int(blk_off[-1]), width, self.block_size, True, self.status)
         cu_k = out["cu_seqlens_k"]
+        items_end = meta.numel() - (b if slots is not None else 0)
         ctx = Context(prefill=True, positions=out["positions"], cu_seqlens_q=out["cu_seqlens_q"], cu_seqlens_k=cu_k,
                       slot_mapping=out["slot_mapping"], max_seqlen_q=int(q_len[:bp].max()),
                       max_seqlen_k=int(seq_len.max()), block_table=out["block_table"], num_decode=num_decode,
-                      cache_seqlens=(cu_k[bp + 1:] - cu_k[bp:-1]).contiguous(), status=self.status)
+                      cache_seqlens=(cu_k[bp + 1:] - cu_k[bp:-1]).contiguous(), status=self.status,
+                      prefill_items=meta[items_end - items.size:items_end].view(-1, 2) if items.size else None,
+                      prefill_item_rows=self.item_rows)
         if slots is None:
             return out["input_ids"], ctx
         return out["input_ids"], ctx, meta[meta.numel() - b:]

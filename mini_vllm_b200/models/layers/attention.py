@@ -51,6 +51,7 @@ class FlashAttention(nn.Module):
         self.sliding_window = tuple(sliding_window)
         # placeholders the executor replaces with views of its KV pool (found by hasattr)
         self.k_cache = self.v_cache = torch.tensor([])
+        self._item_rows = None            # query-block size of the prefill kernel's work items for this head layout
 
     @property
     def window_left(self) -> int:
@@ -87,6 +88,14 @@ class FlashAttention(nn.Module):
                                   k_in_place=ctx.prefill and ctx.block_table is None, status=ctx.status)
         return self._attend(ctx, q, k, v)
 
+    def _items(self, ctx: Context):
+        """The step's prefill work list, if the packing step built one for this layer's query-block size."""
+        if ctx.prefill_items is None:
+            return None
+        if self._item_rows is None:
+            self._item_rows = ops.prefill_item_rows(self.num_heads, self.num_kv_heads, self.head_dim)
+        return ctx.prefill_items if ctx.prefill_item_rows == self._item_rows else None
+
     def _attend_mixed(self, ctx: Context, q: torch.Tensor) -> torch.Tensor:
         """A step holding both kinds of sequence (an extension; the reference's Context is one or the
         other): the prompts go through the prefill kernel, the single-token sequences at the end through
@@ -96,7 +105,7 @@ class FlashAttention(nn.Module):
         out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         ops.prefill_attn(q[:tp], self.k_cache, self.v_cache, ctx.cu_seqlens_q[:bp + 1], ctx.cu_seqlens_k[:bp + 1],
                          ctx.max_seqlen_q, self.scaling, self.window_left, block_table=ctx.block_table[:bp],
-                         out=out[:tp], status=ctx.status)
+                         out=out[:tp], status=ctx.status, items=self._items(ctx))
         wl = self.window_left
         table = ctx.block_table[bp:]
         ws = ctx.decode_plans.get(wl)
@@ -116,9 +125,9 @@ class FlashAttention(nn.Module):
             if ctx.block_table is not None:        # prefix cache in play: keys come from the pool
                 return ops.prefill_attn(q, self.k_cache, self.v_cache, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
                                         ctx.max_seqlen_q, self.scaling, self.window_left,
-                                        block_table=ctx.block_table, status=ctx.status)
+                                        block_table=ctx.block_table, status=ctx.status, items=self._items(ctx))
             return ops.prefill_attn(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q, self.scaling,
-                                    self.window_left, status=ctx.status)
+                                    self.window_left, status=ctx.status, items=self._items(ctx))
         # decode: q [B,Hq,D] -> [B,1,Hq,D] like flash_attn_with_kvcache on q.unsqueeze(1)
         wl = self.window_left
         ws = ctx.decode_plans.get(wl)

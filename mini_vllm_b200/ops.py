@@ -261,11 +261,39 @@ def decode_attn_static(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     return out
 
 
+def prefill_item_rows(num_q_heads: int, num_kv_heads: int, head_dim: int) -> int:
+    """Rows of q that one work item of the prefill kernel covers (128 or 256; a property of the head layout)."""
+    rows = _cabi.load().mvb_prefill_item_rows(num_q_heads, num_kv_heads, head_dim)
+    _cabi.check(min(rows, 0), "mvb_prefill_item_rows")
+    return rows
+
+
+def build_prefill_items(q_lens, k_lens, item_rows: int):
+    """The work list of a prefill launch: int32 [n, 2] of (sequence, query block), every query block of every
+    sequence once, the blocks that see the most keys first (the order in which the GPU takes them).  Pure host
+    arithmetic on the per-sequence lengths the packing step already has; numpy in, numpy out."""
+    import numpy as np
+    q_lens = np.asarray(q_lens, np.int64)
+    k_lens = np.asarray(k_lens, np.int64)
+    n_qb = (q_lens + item_rows - 1) // item_rows
+    seq = np.repeat(np.arange(q_lens.size, dtype=np.int64), n_qb)
+    first = np.cumsum(n_qb) - n_qb
+    qb = np.arange(int(n_qb.sum()), dtype=np.int64) - np.repeat(first, n_qb)
+    # keys visible to the block's last row: its position + 1
+    visible = k_lens[seq] - q_lens[seq] + np.minimum((qb + 1) * item_rows, q_lens[seq])
+    order = np.argsort(-visible, kind="stable")
+    return np.stack([seq[order], qb[order]], axis=1).astype(np.int32)
+
+
 def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
                  cu_seqlens_k: torch.Tensor, max_seqlen_q: int, scale: float, window_left: int = -1,
                  block_table: torch.Tensor | None = None, out: torch.Tensor | None = None,
-                 status: torch.Tensor | None = None) -> torch.Tensor:
-    """q [Tq,Hq,D]; k/v dense [Tk,Hkv,D] (block_table None) or the paged pool [blocks,bs,Hkv,D]."""
+                 status: torch.Tensor | None = None, items: torch.Tensor | None = None) -> torch.Tensor:
+    """q [Tq,Hq,D]; k/v dense [Tk,Hkv,D] (block_table None) or the paged pool [blocks,bs,Hkv,D].
+
+    ``items`` (int32 [n, 2] on the device, from ``build_prefill_items``) gives the launch its work as a list of
+    (sequence, query block) pairs instead of a grid over the longest sequence's block count: same result, no
+    empty block indices, the longest blocks first."""
     _need(q, torch.bfloat16, "q"); _heads_contiguous(q, "q")
     _need(cu_seqlens_q, torch.int32, "cu_seqlens_q"); _need(cu_seqlens_k, torch.int32, "cu_seqlens_k")
     Tq, hq, d = q.shape
@@ -279,6 +307,16 @@ def prefill_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q
         kv_rows, k_stride, v_stride, tstride = nblk * bs, hkv * d, hkv * d, block_table.stride(0)
     if out is None:
         out = torch.empty(Tq, hq, d, dtype=torch.bfloat16, device=q.device)
+    if items is not None and 0 < items.shape[0] <= 65535:
+        _need(items, torch.int32, "items")
+        assert items.dim() == 2 and items.shape[1] == 2 and items.is_contiguous()
+        rc = _cabi.load().mvb_prefill_attn_items(
+            _ptr(q), q.stride(0), _ptr(k), k_stride, _ptr(v), v_stride, kv_rows, _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
+            _ptr(block_table), tstride, bs, cu_seqlens_q.numel() - 1, Tq, int(max_seqlen_q), hq, hkv, d, float(scale),
+            window_left, _ptr(out), out.stride(0), _ptr(items), items.shape[0], _ptr(status), _stream())
+        _cabi.check(rc, "mvb_prefill_attn_items")
+        LaunchCounter.add(1)
+        return out
     rc = _cabi.load().mvb_prefill_attn(
         _ptr(q), q.stride(0), _ptr(k), k_stride, _ptr(v), v_stride, kv_rows, _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
         _ptr(block_table), tstride, bs, cu_seqlens_q.numel() - 1, Tq, int(max_seqlen_q), hq, hkv, d, float(scale),

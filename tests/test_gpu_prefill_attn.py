@@ -14,6 +14,21 @@ def cu(lens):
     return torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32)
 
 
+def with_work_list(cuda, out, q_lens, k_lens, hq, hkv, d, call):
+    """The same launch with its work given as a list (every case of this file runs both ways): bit-identical to
+    the plain grid, also when the list comes in another order."""
+    import numpy as np
+    items = ops.build_prefill_items(q_lens, k_lens, ops.prefill_item_rows(hq, hkv, d))
+    assert sorted(map(tuple, items.tolist())) == [(s, b) for s, n in enumerate(q_lens)
+                                                  for b in range(cdiv(n, ops.prefill_item_rows(hq, hkv, d)))]
+    for order in (items, items[::-1].copy()):
+        status = ops.new_status(cuda)
+        listed = call(torch.from_numpy(order).to(cuda), status)
+        torch.cuda.synchronize()
+        ops.check_status(status)
+        assert torch.equal(listed, out), "the work-list launch differs from the grid launch"
+
+
 def run_dense(cuda, lens, hq, hkv, d, window_left=-1, seed=0, packed_qkv=False):
     g = generator(seed)
     T = sum(lens)
@@ -32,6 +47,9 @@ def run_dense(cuda, lens, hq, hkv, d, window_left=-1, seed=0, packed_qkv=False):
     torch.cuda.synchronize()
     ops.check_status(status)
     assert_close_attn(out, want, f"prefill dense lens={lens[:4]}.. hq={hq} hkv={hkv} d={d} w={window_left}")
+    with_work_list(cuda, out, lens, lens, hq, hkv, d,
+                   lambda items, st: ops.prefill_attn(qd, kd, vd, cq.to(cuda), cq.to(cuda), max(lens), d ** -0.5,
+                                                      window_left, status=st, items=items))
 
 
 def run_paged(cuda, q_lens, k_lens, hq, hkv, d, window_left=-1, seed=0, tables=None, num_blocks=None, g=None):
@@ -43,11 +61,15 @@ def run_paged(cuda, q_lens, k_lens, hq, hkv, d, window_left=-1, seed=0, tables=N
     cq, ck, bt = cu(q_lens), cu(k_lens), table_tensor(tables)
     want = oattn.prefill(q, k_pool, v_pool, cq, ck, block_table=bt, window_left=window_left)
     status = ops.new_status(cuda)
-    out = ops.prefill_attn(q.to(cuda), k_pool.to(cuda), v_pool.to(cuda), cq.to(cuda), ck.to(cuda), max(q_lens),
+    qd, kd, vd = q.to(cuda), k_pool.to(cuda), v_pool.to(cuda)
+    out = ops.prefill_attn(qd, kd, vd, cq.to(cuda), ck.to(cuda), max(q_lens),
                            d ** -0.5, window_left, block_table=bt.to(cuda), status=status)
     torch.cuda.synchronize()
     ops.check_status(status)
     assert_close_attn(out, want, f"prefill paged q={q_lens[:4]}.. k={k_lens[:4]}.. d={d} w={window_left}")
+    with_work_list(cuda, out, q_lens, k_lens, hq, hkv, d,
+                   lambda items, st: ops.prefill_attn(qd, kd, vd, cq.to(cuda), ck.to(cuda), max(q_lens), d ** -0.5,
+                                                      window_left, block_table=bt.to(cuda), status=st, items=items))
 
 
 def test_single_short_sequence(cuda):
@@ -149,3 +171,22 @@ def test_logits_that_jump_between_key_tiles(cuda, boost):
     torch.cuda.synchronize()
     ops.check_status(status)
     assert_close_attn(out, want, f"logit jumps x{boost}")
+
+
+def test_work_list_entries_outside_the_batch_are_skipped(cuda):
+    """A list with entries that name no query block of the batch (a sequence or a block past the end) plus every real
+    block: the real ones are computed, the others skipped, nothing is reported."""
+    import numpy as np
+    g = generator(5)
+    lens = [300, 40, 700]
+    q, k, v = randn_bf16(g, sum(lens), 16, 128), randn_bf16(g, sum(lens), 8, 128), randn_bf16(g, sum(lens), 8, 128)
+    cq = cu(lens).to(cuda)
+    qd, kd, vd = q.to(cuda), k.to(cuda), v.to(cuda)
+    ref = ops.prefill_attn(qd, kd, vd, cq, cq, max(lens), 128 ** -0.5)
+    items = ops.build_prefill_items(lens, lens, ops.prefill_item_rows(16, 8, 128))
+    noisy = np.concatenate([np.array([[7, 0], [1, 5], [-1, 0], [0, -2]], np.int32), items]).astype(np.int32)
+    status = ops.new_status(cuda)
+    out = ops.prefill_attn(qd, kd, vd, cq, cq, max(lens), 128 ** -0.5, status=status, items=torch.from_numpy(noisy).to(cuda))
+    torch.cuda.synchronize()
+    ops.check_status(status)
+    assert torch.equal(out, ref)
