@@ -81,7 +81,7 @@ struct PrefillCfg {
   // after the tiles: barriers, the tensor-memory address, the failure flag, two item slots and the
   // launch-control response
   static constexpr int CTRL_BYTES = 512;
-  static constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_FAIL = OFF_TMEM_SLOT + 4, OFF_ITEMS = 256, OFF_CLC = 288;
+  static constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_FAIL = OFF_TMEM_SLOT + 4, OFF_ITEMS = 256, OFF_CLC = 352;
   static constexpr int STAGE_BYTES = NQ * 4 * 4096;     // a 32-row x 128-byte output staging tile per softmax warp
   static constexpr int SMEM = NQ * Q_BYTES + 4 * KV_BYTES + 1024 /*align*/ + CTRL_BYTES + STAGE_BYTES;
   static constexpr int TMEM_COLS = NQ * (BN + D) <= 256 ? 256 : 512;   // power of two
@@ -104,26 +104,34 @@ struct PrefillItem {
   // indices are handed out x-fastest, so every sequence's last query block (the one with the most
   // keys) is worked on before any second-to-last one, which keeps the tail of the launch short.
   // With an item list: grid = (heads or head pairs, items), the list's order is the order of the work.
+  // what the producer hands on with a listed item, so that the other roles read no global memory for it
+  int seq_in, qb_in, q_begin_in, q_end_in, k_begin_in, k_end_in;
+
   __device__ __forceinline__ void init(const PrefillParams& p, int bx, int by, int bz) {
+    int s_ = by, qb_ = 0;
+    if constexpr (LIST) {
+      s_ = p.items[2 * by];
+      qb_ = p.items[2 * by + 1];
+      if (s_ < 0 || s_ >= p.num_seqs) { s_ = 0; qb_ = -1; }      // a bad entry comes out as an empty item
+    }
+    init_from(p, bx, bz, s_, qb_, p.cu_q[s_], p.cu_q[s_ + 1], p.cu_k[s_], p.cu_k[s_ + 1]);
+  }
+
+  __device__ __forceinline__ void init_from(const PrefillParams& p, int bx, int bz, int s_, int listed_qb, int q_begin,
+                                            int q_end, int k_begin, int k_end) {
+    seq_in = s_; qb_in = listed_qb; q_begin_in = q_begin; q_end_in = q_end; k_begin_in = k_begin; k_end_in = k_end;
+    s = s_;
     const bool pair = p.pair_heads != 0;
     // The NQ query tiles of an item are either NQ heads of one GQA group over the same 128 rows (each
     // K/V tile loaded once serves them all: half the K/V traffic per flop) or, without a group to
     // share, NQ consecutive 128-row tiles of one head.
-    int listed_qb = 0;
-    if constexpr (LIST) {
-      s = p.items[2 * by];
-      listed_qb = p.items[2 * by + 1];
-      if (s < 0 || s >= p.num_seqs) { s = 0; listed_qb = -1; }   // a bad entry comes out as an empty item
-    } else {
-      s = by;
-    }
     const int qh0 = pair ? bx * NQ : bx;
     kvh = qh0 / p.group;
     const int rows_per_item = pair ? 128 : 128 * NQ;
-    q0 = p.cu_q[s];
-    k0 = p.cu_k[s];
-    const int q_len = p.cu_q[s + 1] - q0;
-    k_len = p.cu_k[s + 1] - k0;
+    q0 = q_begin;
+    k0 = k_begin;
+    const int q_len = q_end - q0;
+    k_len = k_end - k0;
     const int n_qb = (q_len + rows_per_item - 1) / rows_per_item;
     const int qb = LIST ? listed_qb : n_qb - 1 - bz;
     empty = qb < 0 || qb >= n_qb;
@@ -177,7 +185,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + C::OFF_TMEM_SLOT);
   volatile uint32_t* fail_flag = reinterpret_cast<uint32_t*>(ctrl + C::OFF_FAIL);
-  volatile int4* items = reinterpret_cast<volatile int4*>(ctrl + C::OFF_ITEMS);   // {x, y, z, valid}
+  volatile int4* items = reinterpret_cast<volatile int4*>(ctrl + C::OFF_ITEMS);   // slots 0-1: {x, y, z, valid}; list form: 2-5 hold each slot's (sequence, block, q bounds), (k bounds)
   const uint32_t clc_resp = smem_u32(ctrl + C::OFF_CLC);
   const uint32_t stage_s = smem_u32(ctrl + C::CTRL_BYTES);
 
@@ -213,6 +221,14 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     const int slot = n & 1;
     if (!wait(B_ITEM_FULL + slot, (n >> 1) & 1, 900)) return false;
     const int x = items[slot].x, y = items[slot].y, z = items[slot].z, valid = items[slot].w;
+    if constexpr (LIST) {
+      const int4 a = const_cast<const int4&>(const_cast<volatile int4&>(items[2 + 2 * slot]));
+      const int4 b = const_cast<const int4&>(const_cast<volatile int4&>(items[3 + 2 * slot]));
+      mbar_arrive(&bars[B_ITEM_FREE + slot]);
+      if (!valid) return false;
+      item.init_from(p, x, z, a.x, a.y, a.z, a.w, b.x, b.y);
+      return true;
+    }
     mbar_arrive(&bars[B_ITEM_FREE + slot]);
     if (!valid) return false;
     item.init(p, x, y, z);
@@ -234,6 +250,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       if (n_pub >= 2) ok = wait(B_ITEM_FREE + slot, ((n_pub >> 1) - 1) & 1, 910);
       if (ok) {
         items[slot].x = x; items[slot].y = y; items[slot].z = z; items[slot].w = valid;
+        if constexpr (LIST) {
+          items[2 + 2 * slot].x = item.seq_in; items[2 + 2 * slot].y = item.qb_in;
+          items[2 + 2 * slot].z = item.q_begin_in; items[2 + 2 * slot].w = item.q_end_in;
+          items[3 + 2 * slot].x = item.k_begin_in; items[3 + 2 * slot].y = item.k_end_in;
+        }
         mbar_arrive(&bars[B_ITEM_FULL + slot]);
       }
     };
