@@ -24,6 +24,10 @@
 //                   passed through two barriers): one tile's products run under the other tile's
 //                   softmax.  The first 64 keys of P_t V are issued outside the turn, while the
 //                   softmax group is still exponentiating the other 64;
+//                   With ONE query tile (head_dim 256: O takes 256 of the 512 columns) there is no
+//                   other tile to fill the pipe during the softmax, but room for a second S buffer:
+//                   S(j) is issued into the buffer that held P(j-2) before P(j-1) is waited for, so it
+//                   runs under the softmax of tile j-1 and the softmax group never waits for S;
 //   softmax groups  one warpgroup per query tile, one thread per row: tcgen05.ld brings the row of
 //                   S into registers (no shuffles), running max / sum, exp2, P back to tensor
 //                   memory, O rescaled in tensor memory only when the running max moved by more
@@ -69,7 +73,7 @@ struct PrefillParams {
 // may issue its next burst.
 enum : int { B_QFULL = 0, B_KFULL = 2, B_VFULL = 4, B_KFREE = 6, B_VFREE = 8, B_SFULL = 10, B_PFULL = 12,
              B_TURN = 28, B_ODONE = 16, B_OFREE = 18, B_VFIXED = 20, B_QFREE = 22, B_ITEM_FULL = 23, B_ITEM_FREE = 25,
-             B_CLC = 27, B_COUNT = 30 };
+             B_CLC = 27, B_PVDONE = 30, B_COUNT = 31 };
 
 template <int D, int BN, int NQ>
 struct PrefillCfg {
@@ -84,10 +88,14 @@ struct PrefillCfg {
   static constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_FAIL = OFF_TMEM_SLOT + 4, OFF_ITEMS = 256, OFF_CLC = 352;
   static constexpr int STAGE_BYTES = NQ * 4 * 4096;     // a 32-row x 128-byte output staging tile per softmax warp
   static constexpr int SMEM = NQ * Q_BYTES + 4 * KV_BYTES + 1024 /*align*/ + CTRL_BYTES + STAGE_BYTES;
-  static constexpr int TMEM_COLS = NQ * (BN + D) <= 256 ? 256 : 512;   // power of two
-  static constexpr int S_COL = 0;                      // S_t at S_COL + t * BN (P_t aliases its first BN/2 columns)
-  static constexpr int O_COL = NQ * BN;                // O_t at O_COL + t * D
-  static_assert(NQ * (BN + D) <= 512, "tensor memory budget");
+  // With one query tile there is room for a second S buffer: the S product of KV tile j + 1 is then issued before
+  // P of tile j is waited for and runs under that tile's softmax (with two tiles the other tile's products do).
+  static constexpr int S_BUFS = NQ == 1 ? 2 : 1;
+  static constexpr int TMEM_COLS = NQ * (S_BUFS * BN + D) <= 256 ? 256 : 512;   // power of two
+  static constexpr int S_COL = 0;                      // S_t, buffer b at S_COL + (t * S_BUFS + b) * BN (P aliases its first BN/2 columns)
+  static constexpr int O_COL = NQ * S_BUFS * BN;       // O_t at O_COL + t * D
+  static_assert(NQ * (S_BUFS * BN + D) <= 512, "tensor memory budget");
+  static_assert(S_BUFS == 1 || BN == 64, "the two-buffer form publishes P once per 64-key tile");
   static_assert(BN % 64 == 0, "P is written in 64-key halves");
   static_assert(OFF_FAIL + 4 <= OFF_ITEMS && OFF_CLC + 16 <= CTRL_BYTES, "control block layout");
 };
@@ -383,7 +391,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       const uint64_t q_desc = umma_desc_sw128(q_s + t * C::Q_BYTES, 16, 1024);
       const uint64_t k_desc0 = umma_desc_sw128(k_s, 16, 1024);
       const uint64_t v_desc0 = umma_desc_sw128(v_s, C::HALF_KV, 1024);
-      const uint32_t s_tm = tmem + C::S_COL + t * BN, o_tm = tmem + C::O_COL + t * D;
+      const uint32_t s_tm = tmem + C::S_COL + t * C::S_BUFS * BN, o_tm = tmem + C::O_COL + t * D;
       uint32_t g = 0;                                         // KV tiles walked (ring position)
       uint32_t n_pv = 0;                                      // PV products issued (P parity)
       uint32_t n_act = 0;                                     // items in which this tile had rows (Q / O parity)
@@ -401,6 +409,55 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         if (rows <= 0) { jlo = 1; jhi = 0; }                  // this tile sits the item out (it still walks the ring)
         const int j_partial = item.k_len / BN;                // first KV tile with rows past the end
         const int n_it = item.n_it, j_lo = item.j_lo;
+        if constexpr (NQ == 1) {
+          // One tile, two S buffers.  Step `it`: S of KV tile j into the buffer that held P of tile j - 2 (its PV
+          // product was issued before, and the pipe runs in order), then, once the softmax group has published
+          // P of tile j - 1, the PV product of that tile; one extra step for the last PV.
+          for (int it = 0; it <= n_it && ok; ++it) {
+            const int j = j_lo + it;
+            const bool body = it < n_it;
+            const int st = g & 1, stp = (g - 1) & 1;
+            if (body) {
+              ok = ready(B_KFULL + st, (g >> 1) & 1, 600);
+              if (ok && j == jlo) ok = ready(B_QFULL + 0, n_act & 1, 610);
+              if (!ok) break;
+              tc_fence_after();
+              const uint32_t buf = n_burst & 1;                // (n_burst counts the S products here)
+              const uint64_t kd = k_desc0 + ((st * C::KV_BYTES) >> 4);
+#pragma unroll
+              for (int ks = 0; ks < D / 16; ++ks) {
+                const uint32_t qo = ((ks >> 2) * C::HALF_Q + (ks & 3) * 32) >> 4, ko = ((ks >> 2) * C::HALF_KV + (ks & 3) * 32) >> 4;
+                umma_bf16_ss(s_tm + buf * BN, q_desc + qo, kd + ko, IDESC_S, ks > 0);
+              }
+              umma_commit(&bars[B_SFULL + buf]);
+              ++n_burst;
+              umma_commit(&bars[B_KFREE + st]);
+              if (it == n_it - 1) umma_commit(&bars[B_QFREE]);
+            }
+            if (it >= 1) {
+              ok = ready(B_VFULL + stp, ((g - 1) >> 1) & 1, 400);
+              if (ok && j - 1 >= j_partial) ok = ready(B_VFIXED + stp, (fix_parity >> stp) & 1, 450);
+              uint32_t first = 1u;
+              if (ok && j - 1 == jlo) {
+                first = 0u;
+                if (n_act > 0) ok = ready(B_OFREE + 0, (n_act - 1) & 1, 460);
+              }
+              const uint32_t pbuf = n_pv & 1;
+              if (ok) ok = ready(B_PFULL + pbuf, (n_pv >> 1) & 1, 500);
+              if (!ok) break;
+              tc_fence_after();
+              const uint64_t vd = v_desc0 + ((stp * C::KV_BYTES) >> 4);
+#pragma unroll
+              for (int ks = 0; ks < BN / 16; ++ks)
+                umma_bf16_ts(o_tm, s_tm + pbuf * BN + ks * 8, vd + ((ks * 2048) >> 4), IDESC_O, ks > 0 ? 1u : first);
+              umma_commit(&bars[B_PVDONE]);                   // a rescale of O waits for it
+              if (j - 1 == jhi) umma_commit(&bars[B_ODONE + 0]);
+              ++n_pv;
+              umma_commit(&bars[B_VFREE + stp]);
+            }
+            if (body) ++g;
+          }
+        } else
         // step `it`: PV of KV tile j - 1, then S of tile j; one extra step for the last PV
         for (int it = 0; it <= n_it && ok; ++it) {
           const int j = j_lo + it;
@@ -477,7 +534,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     const int t = warp >> 2;
     const int row = tid & 127;                                // row of the tile = TMEM lane
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const uint32_t s_addr = lane_addr + C::S_COL + t * BN;
+    const uint32_t s_base = lane_addr + C::S_COL + t * C::S_BUFS * BN;
     const uint32_t o_addr = lane_addr + C::O_COL + t * D;
     uint32_t n_s = 0, n_epi = 0;                              // S tiles consumed (S / P parity), epilogues done (O parity)
     bool ok = true;
@@ -500,7 +557,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       const int n_itt = jhi_me - jlo_me + 1;
       for (int itt = 0; itt < n_itt && ok; ++itt, ++n_s) {
         const int j = jlo_me + itt, col0 = j * BN;
-        ok = wait(B_SFULL + t, n_s & 1, 700);
+        const uint32_t sbuf = C::S_BUFS == 2 ? (n_s & 1) : 0u;    // which S buffer this tile is in
+        const uint32_t s_addr = s_base + sbuf * BN;
+        ok = C::S_BUFS == 2 ? wait(B_SFULL + sbuf, (n_s >> 1) & 1, 700) : wait(B_SFULL + t, n_s & 1, 700);
         if (!ok) break;
         tc_fence_after();
         // Visible keys of this row inside the tile: [vis_lo, vis_hi] relative to col0.  The rows of a
@@ -534,6 +593,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             alpha = fast_exp2(m_run - m_use);                 // m_run = -inf -> 0
           }
           if (itt > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+            if constexpr (C::S_BUFS == 2) {
+              // this tile's S was issued BEFORE the PV product of the previous tile (the n_s-th of this group,
+              // counted from 1): O is ours only when that product has completed
+              ok = wait(B_PVDONE, (n_s - 1) & 1, 710);
+              tc_fence_after();
+            }
 #pragma unroll 1
             for (int c = 0; c < D / 16; ++c) {                // rare: small chunks, to stay short of registers
               uint32_t r[16];
@@ -553,7 +618,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             tmem_wait_st();                                   // warp-wide: every lane's words are in tensor memory
             if (lane == 0) {
               tc_fence_before();
-              mbar_arrive(&bars[B_PFULL + 2 * t + (c >> 1)]);
+              mbar_arrive(&bars[C::S_BUFS == 2 ? B_PFULL + sbuf : B_PFULL + 2 * t + (c >> 1)]);
             }
           }
         };
